@@ -1,0 +1,128 @@
+/*
+ * wush_int4.h -- C ABI of the B200 (sm_100a) INT4 W4A4 linear-layer kernels.
+ *
+ * Library: wush_int4_kernel_b200/libwush_int4_b200.so (nvcc, no torch dependency).
+ *
+ * Every entry point below is what the reference project's Python binding for the
+ * same operator would call; the reference item each one replaces is cited as
+ * file:line of rib12316/WUSH_int4_kernel.  The torch-facing module `my_int4._C`
+ * of this repository is a thin C++ layer over exactly these functions.
+ *
+ * Conventions
+ *   - All data pointers are DEVICE pointers on the current CUDA device, row-major,
+ *     contiguous.  bf16 / fp16 are passed as `void*` (2-byte elements).
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *   - Calls are asynchronous, never synchronise the host and never allocate
+ *     device memory: scratch is passed in by the caller.  They are therefore
+ *     safe to capture in a CUDA Graph.  One-time function-attribute set-up
+ *     happens inside wush_init(), which must run once per device OUTSIDE capture
+ *     (the other entry points call it lazily on first use).
+ *   - Return value: WUSH_OK or an error code; wush_last_error() gives the text of
+ *     the calling thread's most recent failure.
+ *
+ * Data formats (identical to the reference, my_int4/rtn_int4.py:53-55):
+ *   packed codes : byte i of a row = (q[2i] & 0xF) | ((q[2i+1] & 0xF) << 4),
+ *                  two's-complement nibbles, even element in the low nibble
+ *   scales       : bf16, one per 32 consecutive K elements
+ *   activations  : xq (M, K/2) u8, xs (M, K/32) bf16
+ *   weights      : wq (N, K/2) u8, ws (N, K/32) bf16
+ *   transform    : t (K/32, 32, 32) bf16, T[g][j][i] multiplies input i into output j
+ *   output       : y (M, N) fp16
+ */
+#ifndef WUSH_INT4_H_
+#define WUSH_INT4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WUSH_ABI_VERSION 1
+
+typedef enum {
+    WUSH_OK = 0,
+    WUSH_ERR_INVALID_ARGUMENT = 1, /* bad size / null pointer / misaligned pointer   */
+    WUSH_ERR_CUDA = 2,             /* a CUDA runtime call or launch failed           */
+    WUSH_ERR_UNSUPPORTED = 3,      /* device is not sm_100, or shape outside limits  */
+    WUSH_ERR_WORKSPACE = 4,        /* scratch buffer missing or too small            */
+    WUSH_ERR_DEVICE_FLAG = 5       /* a kernel reported a bounded-wait timeout       */
+} wush_status;
+
+int wush_abi_version(void);
+const char* wush_last_error(void);
+
+/* One-time per-device set-up (kernel attributes, driver entry points).  Call once
+ * per device before any stream capture.  Fails with WUSH_ERR_UNSUPPORTED when the
+ * current device is not compute capability 10.x. */
+int wush_init(void);
+
+/* --- a1: sigma-clip G=32 INT4 quantisation --------------------------------------
+ * Replaces quant_int4 (csrc/quant_int4.cu:109-134); bit-exact with
+ * rtn_int4.quant_int4 (my_int4/rtn_int4.py:33-55).
+ * x: n_groups*32 bf16;  q: n_groups*16 bytes;  s: n_groups bf16. */
+int wush_quant_int4(const void* x, int64_t n_groups, uint8_t* q, void* s, void* stream);
+
+/* --- a4..a7: fused WUSH block transform + quantisation ----------------------------
+ * x'_j = sum_i x_i * T[g][j][i] in fp32, then the a1 chain on the un-rounded x'.
+ * Replaces fused_transform_quant_int4 (csrc/fused_tq_int4.cu:87-118, variant EXACT),
+ * _wmma (csrc/fused_tq_wmma.cu:131-162), _v3 (csrc/fused_tq_v3.cu:109-140) and
+ * _smallm (csrc/fused_tq_smallm.cu:89-121).
+ *   WUSH_TQ_EXACT : serial fp32 arithmetic in the reference's order; bit-exact with
+ *                   the fp32 mirror (tests/test_sw2.py:12-24 of the reference).
+ *   WUSH_TQ_FAST  : tensor-core transform + warp-shuffle statistics; differs from
+ *                   EXACT only by rare +-1 code flips (accumulation order).
+ * x: rows*K bf16;  t: (K/32)*1024 bf16;  q: rows*K/2;  s: rows*K/32 bf16. */
+typedef enum { WUSH_TQ_EXACT = 0, WUSH_TQ_FAST = 1 } wush_tq_variant;
+int wush_fused_transform_quant_int4(const void* x, const void* t, int64_t rows, int64_t K,
+                                    int variant, uint8_t* q, void* s, void* stream);
+
+/* --- a8..a10: group-scaled W4A4 product ---------------------------------------------
+ * Y[m][n] = sum_g sx[m][g] * sw[n][g] * P_g,  P_g = sum_{k in g} qa*qw exact in int32,
+ * fp32 accumulation over groups, fp16 output.
+ * Replaces w4a4_gemm_s4 (csrc/gemm_s4.cu:320-379), w4a4_gemm / _v1 / _v2
+ * (csrc/gemm_int4.cu:89-130, csrc/gemm_wmma.cu:128-172, csrc/gemm_wmma2.cu:141-181),
+ * w4a4_gemv and w4a4_gemv_multi (csrc/gemv_int4.cu:145-223).
+ *   WUSH_GEMM_AUTO   : pick by M (decode kernels for M <= 32, tile GEMM above)
+ *   WUSH_GEMM_GEMV   : CUDA-core streaming kernel (M <= 4)
+ *   WUSH_GEMM_DECODE : tensor-core streaming kernel, weights as the wide operand (M <= 32)
+ *   WUSH_GEMM_TILE   : tiled tensor-core GEMM (any M)
+ * K % 32 == 0.  `workspace` may be NULL when wush_w4a4_gemm_workspace_bytes() is 0. */
+typedef enum {
+    WUSH_GEMM_AUTO = 0,
+    WUSH_GEMM_GEMV = 1,
+    WUSH_GEMM_DECODE = 2,
+    WUSH_GEMM_TILE = 3
+} wush_gemm_variant;
+size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
+int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws,
+                   int64_t M, int64_t N, int64_t K, void* y, int variant, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/* --- a11: tensor-core self-tests ------------------------------------------------------
+ * wush_i8_atom_selftest replaces s4_atom_selftest (csrc/gemm_s4.cu:50-82):
+ * a (8,32) int8 in [-8,7], b (32,8) int8 -> c (8,8) int32 through one int8 MMA atom.
+ * wush_group_partials exposes the exact per-group partial sums P[m][n][g] (int32)
+ * produced by the same tensor-core code path the GEMM uses (test-only; M*N*K/32 ints). */
+int wush_i8_atom_selftest(const int8_t* a, const int8_t* b, int32_t* c, void* stream);
+int wush_group_partials(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N, int64_t K,
+                        int32_t* P, void* stream);
+
+/* --- per-tensor route ("next" row 1) ------------------------------------------------------
+ * q = clamp(rint(x * inv_scale), -7, 7); inv_scale from the host value, or from device
+ * memory when inv_scale_dev != NULL.  Replaces quant_int4_tensor_scale{,_dev}
+ * (csrc/fast_path.cu:42-63, 92-109).  n % 32 == 0. */
+int wush_quant_int4_tensor_scale(const void* x, int64_t n, float inv_scale,
+                                 const float* inv_scale_dev, uint8_t* q, void* stream);
+/* y = fp16(alpha * sum_k qa*qw) with full-K int32 accumulation; alpha from the host
+ * value or from device memory when alpha_dev != NULL.  Replaces w4a4_gemm_cutlass{,_dev}
+ * (csrc/gemm_cutlass_int4.cu:132-188). */
+int wush_w4a4_gemm_tensor_scale(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N,
+                                int64_t K, float alpha, const float* alpha_dev, void* y,
+                                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WUSH_INT4_H_ */

@@ -1,0 +1,58 @@
+"""ctypes view of ``libwush_int4_b200.so`` -- the C ABI declared in ``include/wush_int4.h``.
+
+This is the boundary a non-Python host would bind.  Pointers are raw device addresses
+(``tensor.data_ptr()``), the stream is a raw ``cudaStream_t``.  Loading fails loudly when the
+library has not been built; nothing here falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libwush_int4_b200.so")
+
+WUSH_OK = 0
+TQ_EXACT, TQ_FAST = 0, 1
+GEMM_AUTO, GEMM_GEMV, GEMM_DECODE, GEMM_TILE = 0, 1, 2, 3
+
+_vp, _i64, _int, _f32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+
+# name -> (restype, argtypes): every symbol include/wush_int4.h declares
+SIGNATURES = {
+    "wush_abi_version": (_int, []),
+    "wush_last_error": (ctypes.c_char_p, []),
+    "wush_init": (_int, []),
+    "wush_quant_int4": (_int, [_vp, _i64, _vp, _vp, _vp]),
+    "wush_fused_transform_quant_int4": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "wush_w4a4_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "wush_w4a4_gemm": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp, _sz, _vp]),
+    "wush_i8_atom_selftest": (_int, [_vp, _vp, _vp, _vp]),
+    "wush_group_partials": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "wush_quant_int4_tensor_scale": (_int, [_vp, _i64, _f32, _vp, _vp, _vp]),
+    "wush_w4a4_gemm_tensor_scale": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp]),
+}
+
+_lib = None
+
+
+class WushError(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m wush_int4_kernel_b200.build`")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)          # AttributeError if a declared symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != WUSH_OK:
+        raise WushError(f"{what}: {load().wush_last_error().decode()} (status {status})")

@@ -1,0 +1,148 @@
+// C-ABI glue: error text, one-time device set-up and the shape dispatcher of wush_w4a4_gemm.
+#include <cstdarg>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace wush {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+
+int fail(int code, const char* fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int check_launch(const char* what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    return WUSH_OK;
+}
+
+// per-device state, set up once (never during stream capture: call wush_init() first)
+constexpr int MAX_DEVICES = 64;
+static std::mutex g_mutex;
+static int g_ready[MAX_DEVICES];        // 0 = not yet, 1 = ok, <0 = -(status)
+static int g_sms[MAX_DEVICES];
+
+int gemv_set_attributes();
+int mma_set_attributes();
+int tc_set_attributes();
+
+static int init_device(int dev)
+{
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "wush_init: cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+        return fail(WUSH_ERR_UNSUPPORTED, "wush_init: device %d is sm_%d%d; this library is built for sm_100a only",
+                    dev, prop.major, prop.minor);
+    g_sms[dev] = prop.multiProcessorCount;
+    if (int s = gemv_set_attributes()) return s;
+    if (int s = mma_set_attributes()) return s;
+    if (int s = tc_set_attributes()) return s;
+    return WUSH_OK;
+}
+
+int ensure_init()
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaGetDevice: %s (is a CUDA device present?)", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(WUSH_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    if (g_ready[dev] == 1) return WUSH_OK;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_ready[dev] == 0) {
+        int s = init_device(dev);
+        g_ready[dev] = (s == WUSH_OK) ? 1 : -s;
+        return s;
+    }
+    if (g_ready[dev] == 1) return WUSH_OK;
+    return fail(-g_ready[dev], "wush_init failed earlier on device %d", dev);
+}
+
+int sm_count()
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return (dev >= 0 && dev < MAX_DEVICES && g_sms[dev] > 0) ? g_sms[dev] : 148;
+}
+
+size_t gemv_smem_bytes(int M, int64_t K);
+int gemv_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
+int mma_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
+bool tc_supported(int64_t M, int64_t N, int64_t K);
+size_t tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int tc_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
+                size_t, cudaStream_t);
+
+// Which kernel a shape runs on.  GEMV: CUDA cores, M <= 4 (the exact per-group scaling costs
+// three instructions per (m, n, group), so beyond a few rows the dot products must move to
+// the tensor cores).  DECODE: weights-as-wide-operand tensor-core streaming, M <= 32.
+// TILE: tcgen05 tile GEMM for everything larger when the shape qualifies.
+static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
+{
+    if (variant != WUSH_GEMM_AUTO) return variant;
+    const bool gemv_ok = gemv_smem_bytes((int)(M < 4 ? M : 4), K) <= 200 * 1024;
+    if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0)) return WUSH_GEMM_GEMV;
+    if (M <= 32) return WUSH_GEMM_DECODE;
+    return tc_supported(M, N, K) ? WUSH_GEMM_TILE : WUSH_GEMM_DECODE;
+}
+
+}  // namespace wush
+
+WUSH_API int wush_abi_version(void) { return WUSH_ABI_VERSION; }
+
+WUSH_API const char* wush_last_error(void) { return wush::g_last_error.c_str(); }
+
+WUSH_API int wush_init(void) { return wush::ensure_init(); }
+
+WUSH_API size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant)
+{
+    using namespace wush;
+    if (M <= 0 || N <= 0 || K <= 0 || K % 32) return 0;
+    int v = resolve_variant(variant, M, N, K);
+    if (v == WUSH_GEMM_TILE && tc_supported(M, N, K)) return tc_workspace_bytes(M, N, K);
+    return 0;
+}
+
+WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M,
+                            int64_t N, int64_t K, void* y, int variant, void* workspace, size_t workspace_bytes,
+                            void* stream)
+{
+    using namespace wush;
+    if (int e = ensure_init()) return e;
+    WUSH_REQUIRE(M >= 0 && N >= 0 && K > 0 && K % 32 == 0, "w4a4_gemm: K must be a positive multiple of 32");
+    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_TILE, "w4a4_gemm: unknown variant %d", variant);
+    if (M == 0 || N == 0) return WUSH_OK;
+    WUSH_REQUIRE(xq && xs && wq && ws && y, "w4a4_gemm: null pointer");
+    WUSH_REQUIRE(aligned16(xq) && aligned16(wq), "w4a4_gemm: packed codes must be 16-byte aligned");
+    WUSH_REQUIRE(N < (1LL << 31) && M < (1LL << 31) && K < (1LL << 31), "w4a4_gemm: dimension too large");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int v = resolve_variant(variant, M, N, K);
+    switch (v) {
+        case WUSH_GEMM_GEMV:
+            WUSH_REQUIRE(M <= 4, "w4a4_gemm: the GEMV variant takes at most 4 rows (got %lld)", (long long)M);
+            if (gemv_smem_bytes((int)M, K) > 200 * 1024)
+                return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm: K=%lld too large for the GEMV variant", (long long)K);
+            return gemv_dispatch(xq, xs, wq, ws, M, N, K, y, st);
+        case WUSH_GEMM_DECODE:
+            return mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
+        case WUSH_GEMM_TILE:
+            if (!tc_supported(M, N, K)) return mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
+            if (workspace_bytes < tc_workspace_bytes(M, N, K) || (tc_workspace_bytes(M, N, K) && !workspace))
+                return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm: workspace of %zu bytes needed, %zu given",
+                            tc_workspace_bytes(M, N, K), workspace_bytes);
+            return tc_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
+    }
+    return fail(WUSH_ERR_INVALID_ARGUMENT, "w4a4_gemm: unknown variant %d", v);
+}

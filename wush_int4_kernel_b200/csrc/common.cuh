@@ -1,0 +1,108 @@
+// Shared helpers for the sm_100a W4A4 kernels: error plumbing of the C ABI, bf16 bit
+// helpers, the exact sigma-clip quantisation chain and nibble unpacking.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+#include <string>
+
+#include "../../include/wush_int4.h"
+
+#define WUSH_API extern "C" __attribute__((visibility("default")))
+
+namespace wush {
+
+// ---- host side: error text of the calling thread ---------------------------------------
+void set_error(const std::string& msg);
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);           // cudaGetLastError -> status
+int ensure_init();                             // lazy wush_init()
+int sm_count();                                // multiprocessors of the current device
+
+#define WUSH_REQUIRE(cond, ...)                                         \
+    do {                                                                \
+        if (!(cond)) return ::wush::fail(WUSH_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- device side ------------------------------------------------------------------------
+// 2.473650 / 7 in fp32: the Gaussian-MSE clip constant of the 15-level INT4 grid.
+#define WUSH_C_CLIP 0.35337862372398376f
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) { return __uint_as_float(b16 << 16); }
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// fp32 -> bf16 bits, round to nearest even (finite inputs and inf; NaN never reaches here
+// because the scale chain maps NaN variance to 1.0).
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+// Scale of one group from its two sums, every operation rounded separately in fp32:
+//   mean = s1/32; var = s2/32 - mean*mean; scale = var>=0 ? sqrt(var)*C + 1e-8 : 1.
+// Returns the bf16 bit pattern; *scale_rt receives the bf16-rounded value as fp32.
+__device__ __forceinline__ uint32_t sigma_clip_scale(float s1, float s2, float* scale_rt) {
+    float mean = __fmul_rn(s1, 0.03125f);            // division by 32 is an exact exponent shift
+    float var = __fsub_rn(__fmul_rn(s2, 0.03125f), __fmul_rn(mean, mean));
+    float scale = 1.0f;
+    if (var >= 0.f) scale = __fadd_rn(__fmul_rn(__fsqrt_rn(var), WUSH_C_CLIP), 1e-8f);
+    uint32_t b = f32_to_bf16_bits(scale);
+    *scale_rt = bf16_bits_to_f32(b);
+    return b;
+}
+
+// Code of one value with IEEE division: clamp(rint(x / scale), -7, 7) as a 4-bit nibble.
+__device__ __forceinline__ uint32_t code_exact(float x, float scale) {
+    int q = __float2int_rn(__fdiv_rn(x, scale));     // saturating conversion, then clamp
+    q = max(-7, min(7, q));
+    return (uint32_t)q & 0xFu;
+}
+
+// The whole bit-exact chain for one group held in registers.
+__device__ __forceinline__ void quant_group_exact(const float (&v)[32], uint4* packed, uint32_t* scale_bits) {
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        s1 = __fadd_rn(s1, v[i]);
+        s2 = __fadd_rn(s2, __fmul_rn(v[i], v[i]));
+    }
+    float scale;
+    *scale_bits = sigma_clip_scale(s1, s2, &scale);
+    uint32_t w[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc |= code_exact(v[b * 8 + e], scale) << (4 * e);
+        w[b] = acc;
+    }
+    *packed = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Eight packed nibbles -> two words of four signed bytes, each byte = 16 * code:
+//   even: codes 0,2,4,6   odd: codes 1,3,5,7.   The factor 16 is undone in the scale.
+__device__ __forceinline__ void unpack_x16(uint32_t w, uint32_t& even, uint32_t& odd) {
+    even = (w << 4) & 0xF0F0F0F0u;
+    odd = w & 0xF0F0F0F0u;
+}
+
+__device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+}  // namespace wush

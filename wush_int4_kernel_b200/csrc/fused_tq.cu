@@ -1,0 +1,217 @@
+// Fused WUSH block transform + sigma-clip INT4 quantisation (C-ABI
+// wush_fused_transform_quant_int4).
+//
+//   x'[r][g][j] = sum_i x[r][g][i] * T[g][j][i]      (fp32, NOT rounded to bf16)
+//   (q, s)      = sigma-clip quantisation of each 32-wide group of x'
+//
+// Two variants behind one entry point:
+//
+// EXACT  (reference fused_transform_quant_int4, csrc/fused_tq_int4.cu:27-85): serial fp32
+//   arithmetic in the reference's order -- i ascending, multiply and add rounded
+//   separately, then the serial statistics -- so the bytes equal the fp32 mirror of the
+//   reference's tests (tests/test_sw2.py:12-24).  One thread per (row, group); a CTA shares
+//   one T block through shared memory (broadcast reads).
+//
+// FAST   (reference _wmma / _v3 / _smallm, csrc/fused_tq_wmma.cu:22-129,
+//   csrc/fused_tq_v3.cu:26-107, csrc/fused_tq_smallm.cu:19-87): one warp owns one group g and
+//   walks down the rows 16 at a time.  The 32x32 block of T lives in registers as the B
+//   operand of bf16 tensor-core MMAs (bf16 products are exact in fp32, accumulation is
+//   fp32), the 16x32 slab of x is the A operand, loaded with one 16-byte load per row per
+//   lane.  The k index inside a group and the order of T's rows are permuted so that
+//     - every operand register comes straight out of a 16-byte load (no shuffles), and
+//     - each lane ends up with 8 CONSECUTIVE outputs of a row, i.e. one 4-byte word of
+//       packed codes, and a quad holds the whole group.
+//   Group statistics are an in-lane sum of 8 plus a two-step xor-shuffle across the quad.
+//   Results differ from EXACT only through summation order (rare +-1 code flips).
+//
+// Algorithmic HBM bytes: 2*M*K (x) + 64*K (T, read once, L2 resident after) + M*K/2 (codes)
+// + M*K/16 (scales).
+#include "common.cuh"
+
+namespace wush {
+
+// ----------------------------------------------------------------------------------------
+// EXACT
+// ----------------------------------------------------------------------------------------
+constexpr int TQE_ROWS = 128;
+
+__global__ void __launch_bounds__(TQE_ROWS)
+fused_tq_exact_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ t,
+                      uint4* __restrict__ q_out, __nv_bfloat16* __restrict__ s_out,
+                      long long rows, int C)
+{
+    __shared__ float4 ts[32 * 8];                         // T[g] as fp32, [j][i]
+    const int g = blockIdx.y;
+    const __nv_bfloat16* tg = t + (size_t)g * 1024;
+    for (int e = threadIdx.x; e < 256; e += TQE_ROWS) {   // 4 elements per step
+        uint2 raw = *reinterpret_cast<const uint2*>(tg + e * 4);
+        ts[e] = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+    }
+    __syncthreads();
+    const long long r = (long long)blockIdx.x * TQE_ROWS + threadIdx.x;
+    if (r >= rows) return;
+
+    float xv[32];
+    const uint4* xg = reinterpret_cast<const uint4*>(x + ((size_t)r * C + g) * 32);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint4 v = xg[c];
+        xv[c * 8 + 0] = bf16_lo(v.x); xv[c * 8 + 1] = bf16_hi(v.x);
+        xv[c * 8 + 2] = bf16_lo(v.y); xv[c * 8 + 3] = bf16_hi(v.y);
+        xv[c * 8 + 4] = bf16_lo(v.z); xv[c * 8 + 5] = bf16_hi(v.z);
+        xv[c * 8 + 6] = bf16_lo(v.w); xv[c * 8 + 7] = bf16_hi(v.w);
+    }
+    float xj[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+            float4 tv = ts[j * 8 + i4];
+            acc = __fadd_rn(acc, __fmul_rn(xv[i4 * 4 + 0], tv.x));
+            acc = __fadd_rn(acc, __fmul_rn(xv[i4 * 4 + 1], tv.y));
+            acc = __fadd_rn(acc, __fmul_rn(xv[i4 * 4 + 2], tv.z));
+            acc = __fadd_rn(acc, __fmul_rn(xv[i4 * 4 + 3], tv.w));
+        }
+        xj[j] = acc;
+    }
+    uint4 packed;
+    uint32_t sbits;
+    quant_group_exact(xj, &packed, &sbits);
+    q_out[(size_t)r * C + g] = packed;
+    s_out[(size_t)r * C + g] = __ushort_as_bfloat16((unsigned short)sbits);
+}
+
+// ----------------------------------------------------------------------------------------
+// FAST
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One row's 8 outputs held by one lane -> statistics over the quad -> one word of codes.
+__device__ __forceinline__ void quantise_row_octet(const float (&v)[8], uint32_t* word, uint32_t* sbits) {
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { s1 += v[e]; s2 = fmaf(v[e], v[e], s2); }
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+    float scale;
+    *sbits = sigma_clip_scale(s1, s2, &scale);
+    const float inv = __frcp_rn(scale);
+    const float magic = 12582912.f;                       // 1.5 * 2^23: low mantissa bits = rint()
+    uint32_t w = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float f = fmaf(v[e], inv, magic);
+        f = fminf(fmaxf(f, magic - 7.f), magic + 7.f);
+        w |= (__float_as_uint(f) & 0xFu) << (4 * e);
+    }
+    *word = w;
+}
+
+__global__ void __launch_bounds__(256)
+fused_tq_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ t,
+                     uint32_t* __restrict__ q_out,        // rows * C * 4 words
+                     __nv_bfloat16* __restrict__ s_out, long long rows, int C, int rows_per_cta)
+{
+    const int warps = blockDim.x >> 5;
+    const int g = blockIdx.x * warps + (threadIdx.x >> 5);
+    if (g >= C) return;                                   // whole warp leaves together
+    const int lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const long long r_begin = (long long)blockIdx.y * rows_per_cta;
+    const long long r_end = min(rows, r_begin + rows_per_cta);
+
+    // B operand: T[g] rows in the permuted order j(nt, n) = 8*(n>>1) + 2*nt + (n&1), n = gid.
+    uint4 bt[4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        const int j = 8 * (gid >> 1) + 2 * nt + (gid & 1);
+        bt[nt] = *reinterpret_cast<const uint4*>(t + (size_t)g * 1024 + j * 32 + tig * 8);
+    }
+
+    const size_t row_stride = (size_t)C * 32;
+    const __nv_bfloat16* xcol = x + (size_t)g * 32 + tig * 8;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+    long long r0 = r_begin;
+    long long ra = r0 + gid, rb = ra + 8;
+    uint4 xa = ra < r_end ? ldg_nc_v4(xcol + ra * row_stride) : zero4;
+    uint4 xb = rb < r_end ? ldg_nc_v4(xcol + rb * row_stride) : zero4;
+    for (; r0 < r_end; r0 += 16) {
+        // prefetch the next slab while this one is in the tensor core
+        const long long na = r0 + 16 + gid, nb = na + 8;
+        uint4 nxa = na < r_end ? ldg_nc_v4(xcol + na * row_stride) : zero4;
+        uint4 nxb = nb < r_end ? ldg_nc_v4(xcol + nb * row_stride) : zero4;
+
+        float acc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+            mma_bf16_16816(acc[nt], xa.x, xb.x, xa.y, xb.y, bt[nt].x, bt[nt].y);
+            mma_bf16_16816(acc[nt], xa.z, xb.z, xa.w, xb.w, bt[nt].z, bt[nt].w);
+        }
+        float va[8], vb[8];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            va[2 * nt] = acc[nt][0]; va[2 * nt + 1] = acc[nt][1];
+            vb[2 * nt] = acc[nt][2]; vb[2 * nt + 1] = acc[nt][3];
+        }
+        uint32_t wa, sa, wb, sb;
+        quantise_row_octet(va, &wa, &sa);                 // all lanes take part in the shuffles
+        quantise_row_octet(vb, &wb, &sb);
+        ra = r0 + gid; rb = ra + 8;
+        if (ra < r_end) {
+            q_out[((size_t)ra * C + g) * 4 + tig] = wa;
+            if (tig == 0) s_out[(size_t)ra * C + g] = __ushort_as_bfloat16((unsigned short)sa);
+        }
+        if (rb < r_end) {
+            q_out[((size_t)rb * C + g) * 4 + tig] = wb;
+            if (tig == 0) s_out[(size_t)rb * C + g] = __ushort_as_bfloat16((unsigned short)sb);
+        }
+        xa = nxa; xb = nxb;
+    }
+}
+
+}  // namespace wush
+
+WUSH_API int wush_fused_transform_quant_int4(const void* x, const void* t, int64_t rows, int64_t K,
+                                             int variant, uint8_t* q, void* s, void* stream)
+{
+    using namespace wush;
+    if (int e = ensure_init()) return e;
+    WUSH_REQUIRE(rows >= 0 && K > 0 && K % 32 == 0, "fused_tq: K must be a positive multiple of 32");
+    WUSH_REQUIRE(variant == WUSH_TQ_EXACT || variant == WUSH_TQ_FAST, "fused_tq: unknown variant %d", variant);
+    if (rows == 0) return WUSH_OK;
+    WUSH_REQUIRE(x && t && q && s, "fused_tq: null pointer");
+    WUSH_REQUIRE(aligned16(x) && aligned16(t) && aligned16(q), "fused_tq: x, t and q must be 16-byte aligned");
+    const int64_t C = K / 32;
+    WUSH_REQUIRE(C <= 65535 * 8, "fused_tq: K too large");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (variant == WUSH_TQ_EXACT) {
+        WUSH_REQUIRE(C <= 65535, "fused_tq(exact): K too large");
+        dim3 grid((unsigned)((rows + TQE_ROWS - 1) / TQE_ROWS), (unsigned)C);
+        fused_tq_exact_kernel<<<grid, TQE_ROWS, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)t,
+                                                         (uint4*)q, (__nv_bfloat16*)s, (long long)rows, (int)C);
+        return check_launch("fused_tq_exact");
+    }
+    // FAST: warps per CTA and rows per CTA chosen so that small M still spreads over the SMs.
+    int warps, rows_per_cta;
+    if (rows <= 32) { warps = 2; rows_per_cta = 32; }
+    else if (rows <= 512) { warps = 4; rows_per_cta = 64; }
+    else { warps = 8; rows_per_cta = 128; }
+    const int64_t gy = (rows + rows_per_cta - 1) / rows_per_cta;
+    WUSH_REQUIRE(gy <= 65535, "fused_tq: too many rows");
+    dim3 grid((unsigned)((C + warps - 1) / warps), (unsigned)gy);
+    fused_tq_fast_kernel<<<grid, warps * 32, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)t,
+                                                      (uint32_t*)q, (__nv_bfloat16*)s, (long long)rows,
+                                                      (int)C, rows_per_cta);
+    return check_launch("fused_tq_fast");
+}
