@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 linear-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows M]
+
+Workload (``config.workload``): the Llama-70B-style fused gate+up decode layer, K=8192,
+N=57344, M=1 activation row per step (``--rows`` changes M).  One step = one layer call as
+the reference times it (bench/exp_p13_official.py:31-39): fused WUSH transform+quantisation
+of the activations, then the group-scaled W4A4 product, replayed from a CUDA Graph.  At
+N GPUs the layer is column parallel: each rank holds N/p output columns (no data-path
+collective; the consumer of a fused gate+up projection is column-local).  Total work is
+fixed, so scaling is "strong".
+
+Prints ONE JSON line: metric effective TOPS (2*M*N*K / time), plus
+  roofline      the weight-streaming product kernel against the measured HBM copy bandwidth
+  cpu_baseline  the CPU oracle port of the same layer on this box's host cores
+  e2e           the same metric through the public ops with HOST activations and results
+  clocks        SM clock / throttle reasons sampled with nvidia-smi while the step runs
+
+``--impl reference`` times the CPU port alone (rank 0 only): the reference's own kernels are
+sm_75-only CUDA and cannot run here, its Python path is what the oracle restates.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_DIM, N_DIM = 8192, 57344
+L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the product kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists).
+PRODUCT_KERNEL_DRAM_BYTES = None
+
+
+def algorithmic_bytes_product(M: int, N: int, K: int) -> int:
+    """codes + scales of the weights and of the activations, fp16 output."""
+    return 9 * N * K // 16 + 9 * M * K // 16 + 2 * M * N
+
+
+def algorithmic_bytes_layer(M: int, N: int, K: int) -> int:
+    """fused transform+quant (x in, T in, codes+scales out) followed by the product."""
+    return 2 * M * K + 64 * K + 2 * (9 * M * K // 16) + 9 * N * K // 16 + 2 * M * N
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the layer (test infrastructure, the only place outside tests and
+# the smoke check where oracle/ is executed)
+# ---------------------------------------------------------------------------------------------
+def cpu_layer_inputs(M: int, n_rows: int, seed: int = 0):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    G = K_DIM // 32
+    wq = rng.integers(0, 256, (n_rows, K_DIM // 2), dtype=np.uint8)
+    ws = np.full((n_rows, G), 0x3C24, np.uint16)                      # bf16 0.01
+    x = (rng.standard_normal((M, K_DIM)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    t = (np.tile(np.eye(32, dtype=np.float32), (G, 1, 1)).view(np.uint32) >> 16).astype(np.uint16)
+    return x, t, wq, ws
+
+
+def time_cpu_layer(M: int, n_rows: int, steps: int, warmup: int):
+    from oracle import w4a4_oracle as orc
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    x, t, wq, ws = cpu_layer_inputs(M, n_rows)
+    for _ in range(warmup):
+        orc.layer(x, t, wq, ws)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        orc.layer(x, t, wq, ws)
+        times.append(time.perf_counter() - t0)
+    return times, cores
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    M = args.rows
+    n_rows = N_DIM                                   # the whole layer: ~0.5 G MAC per row of X
+    times, cores = time_cpu_layer(M, n_rows, args.steps, args.warmup)
+    total = sum(times)
+    tops = 2.0 * M * n_rows * K_DIM * len(times) / total / 1e12
+    line = {
+        "impl": "reference", "metric": "w4a4_layer_eff_tops", "value": tops, "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int4", "data": "synthetic",
+        "config": {"workload": f"llama70b_gate_up_decode K={K_DIM} N={N_DIM} M={M}", "K": K_DIM, "N": N_DIM, "M": M},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
+                         "sample": f"whole layer (N={n_rows} rows of W), {len(times)} steps, OpenMP over output columns"},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from wush_int4_kernel_b200 import _C, synth, timing
+    from wush_int4_kernel_b200.linear import quantise_activations, shard_bounds, w4a4_product
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _C.init()
+
+    M = args.rows
+    n0, n1 = shard_bounds(N_DIM, world, rank, 128)
+    n_local = n1 - n0
+
+    # ---- synthetic layer shard, generated on the GPU (seeded; distributions of synth.py) ----
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    outliers = synth.outlier_channels(K_DIM, torch.Generator(device=dev).manual_seed(7))
+    x_cal = synth.draw_activations(synth.CALIB_ROWS, K_DIM, outliers, gen).float()
+    from wush_int4_kernel_b200 import wush_transform as wt
+    w0 = (0.02 * torch.randn(4096, K_DIM, generator=gen, device=dev)).to(torch.bfloat16)
+    t64 = wt.solve_from_grams(wt.diag_block_gram(x_cal) / synth.CALIB_ROWS, wt.diag_block_gram(w0) / 4096)
+    t_bf16 = t64.to(torch.bfloat16).contiguous()
+    shard_bytes = n_local * (K_DIM // 2 + K_DIM // 16)
+    copies = 1 if shard_bytes > 2 * L2_BYTES else -(-(2 * L2_BYTES + shard_bytes) // shard_bytes)
+    weights = []
+    for _ in range(copies):
+        wq_parts, ws_parts = [], []
+        for r0 in range(0, n_local, 8192):
+            w = (0.02 * torch.randn(min(8192, n_local - r0), K_DIM, generator=gen, device=dev)).to(torch.bfloat16)
+            q, s = _C.quant_int4(wt.transform_weights(w, t64).to(torch.bfloat16).contiguous())
+            wq_parts.append(q)
+            ws_parts.append(s)
+        weights.append((torch.cat(wq_parts).contiguous(), torch.cat(ws_parts).contiguous()))
+    x = synth.draw_activations(M, K_DIM, outliers, gen)
+
+    def make_step(wq, ws):
+        def step():
+            xq, xs = quantise_activations(x, t_bf16)
+            return w4a4_product(xq, xs, wq, ws)
+        return step
+
+    graphs = [timing.capture(make_step(wq, ws))[0] for (wq, ws) in weights]
+    launches_per_step = 2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: W warm-ups, exactly K timed steps, max over ranks -----------
+    sampler = timing.ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.__enter__()
+    for i in range(max(args.warmup, 3)):
+        graphs[i % copies].replay()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        graphs[i % copies].replay()
+    stop.record()
+    barrier()
+    ms_total = start.elapsed_time(stop)
+    # keep the same load running long enough for nvidia-smi to see it (not part of any number)
+    t_end = time.perf_counter() + 1.0
+    while time.perf_counter() < t_end:
+        for i in range(200):
+            graphs[i % copies].replay()
+        torch.cuda.synchronize()
+    if sampler:
+        sampler.__exit__(None, None, None)
+    if world > 1:
+        tmax = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms_total = float(tmax.item())
+    ms_per_step = ms_total / args.steps
+    tops = 2.0 * M * N_DIM * K_DIM / (ms_per_step * 1e-3) / 1e12
+
+    # ---- dominant kernel alone (roofline): the product kernel over the same shard -----------
+    xq, xs = quantise_activations(x, t_bf16)
+    prod_graphs = [timing.capture(lambda wq=wq, ws=ws: w4a4_product(xq, xs, wq, ws))[0] for (wq, ws) in weights]
+    for i in range(5):
+        prod_graphs[i % copies].replay()
+    reps = max(20, min(args.steps, 400))
+    samples = []
+    for _ in range(5):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            prod_graphs[i % copies].replay()
+        e1.record()
+        torch.cuda.synchronize()
+        samples.append(e0.elapsed_time(e1) / reps)
+    kernel_ms = statistics.median(samples)
+    alg_bytes = algorithmic_bytes_product(M, n_local, K_DIM)
+    peak, peak_kind = measured_hbm_peak()
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": PRODUCT_KERNEL_DRAM_BYTES, "peak_kind": f"of {peak_kind}", "kernel": "w4a4 product",
+                "kernel_us": kernel_ms * 1e3, "algorithmic_bytes": alg_bytes}
+
+    # ---- end to end through the public ops: host activations in, host result out -------------
+    x_host = [synth.draw_activations(M, K_DIM, outliers, gen).cpu().pin_memory() for _ in range(4)]
+    y_host = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
+    x_dev = torch.empty(M, K_DIM, dtype=torch.bfloat16, device=dev)
+
+    def e2e_step(i):
+        x_dev.copy_(x_host[i % 4], non_blocking=True)
+        wq, ws = weights[i % copies]
+        a, b = quantise_activations(x_dev, t_bf16)
+        y_host.copy_(w4a4_product(a, b, wq, ws), non_blocking=True)
+
+    for i in range(max(args.warmup, 3)):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        tmax = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tmax.item())
+    e2e_tops = 2.0 * M * N_DIM * K_DIM / (e2e_ms / args.steps * 1e-3) / 1e12
+    e2e = {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": 2 * M * K_DIM * world,
+           "d2h_bytes_per_step": 2 * M * N_DIM, "us_per_step": 1e3 * e2e_ms / args.steps}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- CPU baseline beside it (rank 0, N=1 only): bounded sample of the same layer ---------
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        t0 = time.perf_counter()
+        times, cores = [], os.cpu_count() or 1
+        first, cores = time_cpu_layer(M, N_DIM, 1, 1)
+        n_rep = int(max(3, min(40, 12.0 / max(first[0], 1e-3))))
+        times, cores = time_cpu_layer(M, N_DIM, n_rep, 0)
+        med = statistics.median(times)
+        cpu = {"value": 2.0 * M * N_DIM * K_DIM / med / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+               "sample": f"whole layer M={M}, median of {n_rep} calls ({time.perf_counter() - t0:.1f} s of CPU work)",
+               "us_per_step": med * 1e6}
+
+    clocks = sampler.summary() if sampler else None
+    line = {
+        "metric": "w4a4_layer_eff_tops", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int4", "data": "synthetic",
+        "config": {"workload": f"llama70b_gate_up_decode K={K_DIM} N={N_DIM} M={M}", "K": K_DIM, "N": N_DIM, "M": M,
+                   "sharding": f"column parallel, {n_local} columns per GPU" if world > 1 else "single GPU",
+                   "l2": ("weights (264 MB) exceed L2" if copies == 1 else
+                          f"{copies} rotating copies of the weight shard exceed 2x L2"),
+                   "timing": "CUDA Graph replay of transform+quant -> product, CUDA events, max over ranks"},
+        "us_per_layer": ms_per_step * 1e3,
+        "layer_hbm_frac": algorithmic_bytes_layer(M, n_local, K_DIM) / (ms_per_step * 1e-3) / 1e9 / peak,
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--rows", type=int, default=1, help="activation rows M per step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 20
+        args.warmup = args.warmup if args.warmup is not None else 3
+        run_reference_arm(args)
+    else:
+        args.steps = args.steps if args.steps is not None else 2000
+        args.warmup = args.warmup if args.warmup is not None else 20
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,163 @@
+"""W4A4 linear layer on top of the ``_C`` operators: the M-dispatch the reference leaves to its
+callers (``bench/exp_p13_official.py:31-39``, ``scripts/run_sm100.py:78-89``) and the
+column- / row-parallel variants for 1/2/4/8 GPUs of one node.
+
+Sharding (none exists in the reference; the composition is pinned by the single-op semantics):
+
+* column parallel -- the rows of ``wq`` / ``ws`` (= columns of Y) are split; X, T and the
+  activation quantisation are replicated; no collective unless the caller asks for the full
+  row (``gather_output=True`` -> one all-gather of ``(M, N/p)`` fp16 blocks);
+* row parallel -- K is split on multiples of 32 so each rank keeps whole transform blocks and
+  whole scale groups; every rank produces a partial ``(M, N)`` product and one all-reduce
+  (sum, fp32) finishes it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+def shard_bounds(total: int, world: int, rank: int, multiple: int = 1) -> tuple[int, int]:
+    """[start, stop) of ``rank``'s share of ``total`` items, cut on multiples of ``multiple``;
+    the first ``rem`` ranks get one extra unit.  Covers ``total`` exactly and in order."""
+    if total % multiple:
+        raise ValueError(f"{total} is not a multiple of {multiple}")
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    units = total // multiple
+    base, rem = divmod(units, world)
+    start = rank * base + min(rank, rem)
+    stop = start + base + (1 if rank < rem else 0)
+    return start * multiple, stop * multiple
+
+
+def _ops():
+    from . import _C          # ImportError when the extension is not built: no fallback
+    return _C
+
+
+def quantise_activations(x: torch.Tensor, t: torch.Tensor):
+    """bf16 activations -> (codes, scales) through the fused transform+quantisation op."""
+    ops = _ops()
+    rows = x.numel() // x.shape[-1]
+    if rows <= 32:
+        return ops.fused_transform_quant_int4_smallm(x, t)
+    return ops.fused_transform_quant_int4_v3(x, t)
+
+
+def w4a4_product(xq, xs, wq, ws):
+    """Shape-dispatched product with the reference's per-shape entry points."""
+    ops = _ops()
+    rows = xq.numel() // xq.shape[-1]
+    if rows == 1:
+        return ops.w4a4_gemv(xq.reshape(1, -1), xs.reshape(1, -1), wq, ws).reshape(1, -1)
+    if rows <= 32:
+        return ops.w4a4_gemv_multi(xq, xs, wq, ws)
+    return ops.w4a4_gemm_s4(xq, xs, wq, ws)
+
+
+@dataclass
+class W4A4Linear:
+    """y = W4A4(x): fused transform+quantisation of x, then the group-scaled product."""
+    t: torch.Tensor        # (K/32, 32, 32) bf16
+    wq: torch.Tensor       # (N, K/2) uint8
+    ws: torch.Tensor       # (N, K/32) bf16
+
+    @property
+    def in_features(self) -> int:
+        return self.wq.shape[1] * 2
+
+    @property
+    def out_features(self) -> int:
+        return self.wq.shape[0]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        xq, xs = quantise_activations(x2, self.t)
+        return w4a4_product(xq, xs, self.wq, self.ws).reshape(*lead, self.out_features)
+
+    def to(self, device) -> "W4A4Linear":
+        return W4A4Linear(self.t.to(device), self.wq.to(device), self.ws.to(device))
+
+
+class ColumnParallelW4A4Linear:
+    """Rank ``rank`` of ``world`` holds output columns ``shard_bounds(N, world, rank, multiple)``."""
+
+    def __init__(self, t, wq, ws, world: int, rank: int, multiple: int = 1, gather_output: bool = False,
+                 group=None):
+        self.full_out = wq.shape[0]
+        self.world, self.rank, self.group, self.gather_output = world, rank, group, gather_output
+        self.n0, self.n1 = shard_bounds(self.full_out, world, rank, multiple)
+        self.local = W4A4Linear(t, wq[self.n0:self.n1].contiguous(), ws[self.n0:self.n1].contiguous())
+        self.bounds = [shard_bounds(self.full_out, world, r, multiple) for r in range(world)]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.local(x)
+        if not self.gather_output or self.world == 1:
+            return y
+        return gather_columns(y, self.bounds, self.group)
+
+
+def gather_columns(y_local: torch.Tensor, bounds, group=None) -> torch.Tensor:
+    """All-gather of column blocks of unequal width into the full ``(…, N)`` tensor."""
+    import torch.distributed as dist
+
+    width = max(b - a for a, b in bounds)
+    lead = y_local.shape[:-1]
+    padded = y_local.new_zeros(*lead, width)
+    padded[..., : y_local.shape[-1]] = y_local
+    parts = [torch.empty_like(padded) for _ in bounds]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([p[..., : b - a] for p, (a, b) in zip(parts, bounds)], dim=-1)
+
+
+class RowParallelW4A4Linear:
+    """Rank ``rank`` holds K-slice ``shard_bounds(K, world, rank, 32)`` of the weights and the
+    matching transform blocks; ``__call__`` takes the local slice of the activations and
+    returns the all-reduced product (fp16, summed in fp32)."""
+
+    def __init__(self, t, wq, ws, world: int, rank: int, group=None, reduce_output: bool = True):
+        K = wq.shape[1] * 2
+        self.world, self.rank, self.group, self.reduce_output = world, rank, group, reduce_output
+        self.k0, self.k1 = shard_bounds(K, world, rank, 32)
+        self.local = W4A4Linear(t[self.k0 // 32:self.k1 // 32].contiguous(),
+                                wq[:, self.k0 // 2:self.k1 // 2].contiguous(),
+                                ws[:, self.k0 // 32:self.k1 // 32].contiguous())
+
+    def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
+        y = self.local(x_local)
+        if not self.reduce_output or self.world == 1:
+            return y
+        import torch.distributed as dist
+
+        acc = y.float()
+        dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.group)
+        return acc.to(torch.float16)
+
+
+class TensorParallelFFN:
+    """Llama-style FFN block: fused gate+up (column parallel, gate and up halves of the same
+    intermediate index on the same rank) -> SiLU(gate) * up -> bf16 -> down (row parallel)."""
+
+    def __init__(self, gate_up: tuple, down: tuple, world: int, rank: int, group=None):
+        t_gu, wq_gu, ws_gu = gate_up           # rows [0, I) = gate, [I, 2I) = up
+        t_d, wq_d, ws_d = down                 # (hidden, I/2) codes
+        inter = wq_gu.shape[0] // 2
+        self.i0, self.i1 = shard_bounds(inter, world, rank, 32)
+        rows = torch.cat((torch.arange(self.i0, self.i1), torch.arange(inter + self.i0, inter + self.i1)))
+        rows = rows.to(wq_gu.device)
+        self.gate_up = W4A4Linear(t_gu, wq_gu[rows].contiguous(), ws_gu[rows].contiguous())
+        self.down = RowParallelW4A4Linear.__new__(RowParallelW4A4Linear)
+        self.down.world, self.down.rank, self.down.group, self.down.reduce_output = world, rank, group, True
+        self.down.k0, self.down.k1 = self.i0, self.i1
+        self.down.local = W4A4Linear(t_d[self.i0 // 32:self.i1 // 32].contiguous(),
+                                     wq_d[:, self.i0 // 2:self.i1 // 2].contiguous(),
+                                     ws_d[:, self.i0 // 32:self.i1 // 32].contiguous())
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        gu = self.gate_up(x)
+        half = gu.shape[-1] // 2
+        h = (torch.nn.functional.silu(gu[..., :half].float()) * gu[..., half:].float()).to(torch.bfloat16)
+        return self.down(h.contiguous())

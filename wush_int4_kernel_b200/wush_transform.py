@@ -60,14 +60,10 @@ def _chol(gram: torch.Tensor) -> torch.Tensor:
             raise RuntimeError("diag-block Gram matrix is not positive definite")
 
 
-def compute_wush_transform(X_cal: torch.Tensor, W: torch.Tensor, group_size: int = 32,
-                           use_hadamard: bool = True) -> torch.Tensor:
-    """X_cal (M, K) calibration activations, W (N, K) weights -> T (K/G, G, G) fp64."""
+def solve_from_grams(g_x: torch.Tensor, g_w: torch.Tensor, use_hadamard: bool = True) -> torch.Tensor:
+    """Closed-form T from per-block second moments, both (K/G, G, G) fp64."""
     hi = torch.float64
-    M, N = X_cal.shape[0], W.shape[0]
-    g_x = diag_block_gram(X_cal, group_size, hi) / M
-    g_w = diag_block_gram(W, group_size, hi) / N
-    l_x, l_w = _chol(g_x), _chol(g_w)
+    l_x, l_w = _chol(g_x.to(hi)), _chol(g_w.to(hi))
     u, s, _ = torch.linalg.svd(l_w.transpose(1, 2) @ l_x)
     # Ascending order: the first Hadamard column is constant, so whatever sits in coordinate 0
     # becomes a common offset of all 32 outputs.  The sigma-clip scale subtracts the group
@@ -76,8 +72,17 @@ def compute_wush_transform(X_cal: torch.Tensor, W: torch.Tensor, group_size: int
     u, s = u.flip(-1), s.flip(-1)
     t = (s.clamp_min(1e-300) ** -0.5).unsqueeze(-1) * (u.transpose(1, 2) @ l_w.transpose(1, 2))
     if use_hadamard:
-        t = hadamard(group_size, hi, t.device) @ t
+        t = hadamard(t.shape[-1], hi, t.device) @ t
     return t
+
+
+def compute_wush_transform(X_cal: torch.Tensor, W: torch.Tensor, group_size: int = 32,
+                           use_hadamard: bool = True) -> torch.Tensor:
+    """X_cal (M, K) calibration activations, W (N, K) weights -> T (K/G, G, G) fp64."""
+    hi = torch.float64
+    g_x = diag_block_gram(X_cal, group_size, hi) / X_cal.shape[0]
+    g_w = diag_block_gram(W, group_size, hi) / W.shape[0]
+    return solve_from_grams(g_x, g_w, use_hadamard)
 
 
 def transform_weights(W: torch.Tensor, T: torch.Tensor) -> torch.Tensor:
