@@ -146,7 +146,7 @@ def run_gpu_arm(args):
     t64 = wt.solve_from_grams(wt.diag_block_gram(x_cal) / synth.CALIB_ROWS, wt.diag_block_gram(w0) / 4096)
     t_bf16 = t64.to(torch.bfloat16).contiguous()
     shard_bytes = n_local * (K_DIM // 2 + K_DIM // 16)
-    copies = 1 if shard_bytes > 2 * L2_BYTES else -(-(2 * L2_BYTES + shard_bytes) // shard_bytes)
+    copies = 1 if shard_bytes >= 2 * L2_BYTES else -(-(2 * L2_BYTES + shard_bytes) // shard_bytes)
     weights = []
     for _ in range(copies):
         wq_parts, ws_parts = [], []
@@ -265,7 +265,7 @@ def run_gpu_arm(args):
         t0 = time.perf_counter()
         times, cores = [], os.cpu_count() or 1
         first, cores = time_cpu_layer(M, N_DIM, 1, 1)
-        n_rep = int(max(3, min(40, 12.0 / max(first[0], 1e-3))))
+        n_rep = int(max(3, min(2000, 12.0 / max(first[0], 1e-3))))
         times, cores = time_cpu_layer(M, N_DIM, n_rep, 0)
         med = statistics.median(times)
         cpu = {"value": 2.0 * M * N_DIM * K_DIM / med / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
