@@ -58,6 +58,11 @@ const char* wush_last_error(void);
  * current device is not compute capability 10.x. */
 int wush_init(void);
 
+/* Kernels that wait on barriers give up after a bounded number of polls and record that in a
+ * library-owned device word instead of hanging.  This call (synchronous: it copies four bytes
+ * from the device) returns the word in *flag and clears it; 0 means no kernel gave up. */
+int wush_device_flag(int* flag);
+
 /* --- a1: sigma-clip G=32 INT4 quantisation --------------------------------------
  * Replaces quant_int4 (csrc/quant_int4.cu:109-134); bit-exact with
  * rtn_int4.quant_int4 (my_int4/rtn_int4.py:33-55).
@@ -106,6 +111,12 @@ int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const v
  * wush_group_partials exposes the exact per-group partial sums P[m][n][g] (int32)
  * produced by the same tensor-core code path the GEMM uses (test-only; M*N*K/32 ints). */
 int wush_i8_atom_selftest(const int8_t* a, const int8_t* b, int32_t* c, void* stream);
+/* One tcgen05.mma kind::i8 instruction tile: a (128,32) int8, b (n,32) int8 ->
+ * d (128,n) int32 = a . b^T, n a multiple of 16 up to 256.  layout_mode 0 is the layout the
+ * GEMM uses; 1 (n <= 64 only) swaps the two descriptor strides and exists for diagnosis.
+ * *status (device int, zeroed by the caller) becomes 1 if the bounded wait gave up. */
+int wush_i8_tile_selftest(const int8_t* a, const int8_t* b, int32_t* d, int n, int layout_mode,
+                          int* status, void* stream);
 int wush_group_partials(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N, int64_t K,
                         int32_t* P, void* stream);
 

@@ -41,6 +41,10 @@ def gemm(xq, xs, wq, ws, variant: int = capi.GEMM_AUTO):
     work = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=xq.device)
     capi.check(lib.wush_w4a4_gemm(xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(), M, N, K, y.data_ptr(),
                                   variant, work.data_ptr() if nbytes else None, nbytes, _stream()), "w4a4_gemm")
+    if nbytes >= 4:                       # the tile kernel reports bounded-wait timeouts in word 0 of its scratch
+        torch.cuda.synchronize()
+        flag = int(work[:4].view(torch.int32).item())
+        assert flag == 0, f"tile GEMM aborted: a bounded wait gave up (role code {flag})"
     return y
 
 
@@ -78,3 +82,13 @@ def gemm_ts(xq, wq, alpha: float, alpha_dev=None):
                                                alpha_dev.data_ptr() if alpha_dev is not None else None, y.data_ptr(),
                                                _stream()), "gemm_ts")
     return y
+
+
+def tile_selftest(a, b, layout_mode: int = 0):
+    lib = capi.load()
+    n = b.shape[0]
+    d = torch.zeros(128, n, dtype=torch.int32, device=a.device)
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    capi.check(lib.wush_i8_tile_selftest(a.data_ptr(), b.data_ptr(), d.data_ptr(), n, layout_mode, status.data_ptr(),
+                                         _stream()), "tile_selftest")
+    return d, int(status.item())

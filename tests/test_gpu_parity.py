@@ -179,6 +179,21 @@ def _assert_close(y: torch.Tensor, y64: np.ndarray, tag):
     assert mx <= REL_TOL, (tag, "max", mx)
 
 
+TILE_SHAPES = [(128, 128, 256), (256, 384, 512), (300, 504, 512), (130, 512, 4096), (33, 64, 256), (129, 8, 256),
+               (1000, 1000, 1024), (512, 4096, 4096)]
+
+
+@pytest.mark.parametrize("shape", TILE_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_gemm_tile_tcgen05_vs_fp64(dev, orc, shape):
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=M + 3 * N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    y = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_TILE)
+    _assert_close(y, y64, shape)
+    y2 = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_DECODE)       # streaming kernel on the same data
+    _assert_close(y2, y64, shape)
+
+
 SHAPES = [(64, 96, 128), (1, 64, 64), (300, 500, 512), (130, 512, 4096), (8, 4096, 4096),   # reference tests/test_p13.py:18
           (257, 33, 96), (8, 8, 32), (4, 100, 256), (2, 77, 512), (3, 64, 96), (17, 130, 768), (32, 256, 1024),
           (5, 129, 256), (33, 64, 256)]
@@ -243,7 +258,9 @@ def test_code_minus_eight_is_sign_extended(dev, orc):
 
 
 def test_group_partials_exact(dev, orc):
-    for (M, N, K) in [(8, 16, 64), (33, 130, 256), (5, 64, 1024), (64, 96, 128)]:
+    # the last three shapes run on the tcgen05 tile path (M > 32, K % 256 == 0, N % 8 == 0)
+    for (M, N, K) in [(8, 16, 64), (33, 130, 256), (5, 64, 1024), (64, 96, 128), (130, 136, 512), (128, 256, 256),
+                      (200, 72, 768)]:
         xq, _, wq, _ = _operands(M, N, K, seed=5, orc=orc)
         P = cabi.group_partials(torch.from_numpy(xq).to(dev), torch.from_numpy(wq).to(dev))
         assert np.array_equal(P.cpu().numpy(), orc.group_partials(xq, wq)), (M, N, K)
@@ -432,3 +449,16 @@ def test_full_size_fused_tq_roundtrip(dev, orc):
     rows = torch.arange(0, 4096, 257, device=dev)
     qo, so = orc.fused_tq(orc.bits(x[rows]), orc.bits(layer.t_bf16))
     assert np.array_equal(qe[rows].cpu().numpy(), qo) and np.array_equal(orc.bits(se[rows]), so)
+
+
+# ------------------------------------------------------------------------------------------
+# tcgen05 plumbing: one kind::i8 instruction tile (descriptor / TMEM / tcgen05.ld mapping)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [16, 64, 128, 256])
+def test_tcgen05_i8_tile(dev, n):
+    rng = np.random.default_rng(n)
+    a = rng.integers(-128, 128, (128, 32), dtype=np.int8)
+    b = rng.integers(-128, 128, (n, 32), dtype=np.int8)
+    d, status = cabi.tile_selftest(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev))
+    assert status == 0, "bounded wait on the MMA barrier gave up"
+    assert np.array_equal(d.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32).T)

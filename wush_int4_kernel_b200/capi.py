@@ -23,11 +23,13 @@ SIGNATURES = {
     "wush_abi_version": (_int, []),
     "wush_last_error": (ctypes.c_char_p, []),
     "wush_init": (_int, []),
+    "wush_device_flag": (_int, [_vp]),
     "wush_quant_int4": (_int, [_vp, _i64, _vp, _vp, _vp]),
     "wush_fused_transform_quant_int4": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "wush_w4a4_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "wush_w4a4_gemm": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp, _sz, _vp]),
     "wush_i8_atom_selftest": (_int, [_vp, _vp, _vp, _vp]),
+    "wush_i8_tile_selftest": (_int, [_vp, _vp, _vp, _int, _int, _vp, _vp]),
     "wush_group_partials": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "wush_quant_int4_tensor_scale": (_int, [_vp, _i64, _f32, _vp, _vp, _vp]),
     "wush_w4a4_gemm_tensor_scale": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp]),

@@ -37,6 +37,7 @@ static int g_sms[MAX_DEVICES];
 int gemv_set_attributes();
 int mma_set_attributes();
 int tc_set_attributes();
+int stream_set_attributes();
 
 static int init_device(int dev)
 {
@@ -50,6 +51,7 @@ static int init_device(int dev)
     if (int s = gemv_set_attributes()) return s;
     if (int s = mma_set_attributes()) return s;
     if (int s = tc_set_attributes()) return s;
+    if (int s = stream_set_attributes()) return s;
     return WUSH_OK;
 }
 

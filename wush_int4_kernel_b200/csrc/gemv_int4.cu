@@ -9,16 +9,17 @@
 //   * a CTA first expands the M activation rows into shared memory as signed bytes
 //     (16 * code, even and odd codes of a group in separate 16-byte vectors, so lanes read
 //     consecutive vectors without bank conflicts) and their scales as fp32 / 256;
-//   * each warp owns TWO weight rows at a time; lane l takes groups l, l+32, ...:
-//     one 16-byte load of codes and one 2-byte load of the scale per row and group, four
-//     groups in flight per lane before the first use (>= 128 B per lane outstanding);
+//   * each warp owns one weight row per trip; lane l takes groups l, l+32, ...: one 16-byte
+//     load of codes and one 2-byte load of the scale per group, eight groups (144 B per lane)
+//     in flight before the first use; the next row's loads are issued before the reduction
+//     of the current one, and the very first ones before the activation prologue;
 //   * a word of 8 nibbles becomes two words of 4 signed bytes with one shift and two ANDs
 //     (byte = 16 * code, no sign extension needed), then dp4a against the activation bytes:
 //     the exact group sum comes out multiplied by 256, which the pre-scaled sx undoes;
 //   * fp32 accumulation over groups per lane, xor-shuffle tree over lanes, fp16 store.
 //
-// The grid is persistent: a whole number of CTAs per SM, each looping over row pairs, so the
-// activation expansion is paid once per CTA.
+// The grid is persistent and sized by the occupancy calculator (every CTA resident), rows are
+// dealt round-robin to the warps: with ~40 warps per SM the last round is ~97 % full.
 // Algorithmic HBM bytes per call: 9*N*K/16 (codes + scales of W) + 9*M*K/16 + 2*M*N.
 #include "common.cuh"
 
@@ -26,6 +27,30 @@ namespace wush {
 
 constexpr int GV_THREADS = 256;
 constexpr int GV_WARPS = GV_THREADS / 32;
+
+// One weight row per warp and trip: lane l owns groups l, l+32, ... (8 per lane and trip, i.e.
+// 144 B of loads in flight per lane).  FIRST is issued before the activation prologue so the
+// weight stream starts while the CTA is still expanding x.
+struct RowLoads {
+    uint4 w[8];
+    unsigned short s[8];
+};
+
+__device__ __forceinline__ void issue_row_loads(RowLoads& r, const uint8_t* __restrict__ wrow,
+                                                const unsigned short* __restrict__ srow, int gb, int lane, int G)
+{
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int g = gb + u * 32 + lane;
+        if (g < G) {
+            r.w[u] = ldg_nc_v4(wrow + (size_t)g * 16);
+            r.s[u] = __ldg(srow + g);
+        } else {
+            r.w[u] = make_uint4(0, 0, 0, 0);
+            r.s[u] = 0;
+        }
+    }
+}
 
 template <int MB>
 __global__ void __launch_bounds__(GV_THREADS)
@@ -42,6 +67,16 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
     uint4* xo = xe + (size_t)MB * G;                                   // [MB][G] odd codes * 16
     float* sxf = reinterpret_cast<float*>(xo + (size_t)MB * G);        // [MB][G] sx / 256
 
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t K2 = (size_t)K >> 1;
+    const int stride = gridDim.x * GV_WARPS;
+    int n = blockIdx.x * GV_WARPS + warp;
+    const unsigned short* ws16 = reinterpret_cast<const unsigned short*>(ws);
+
+    // start the weight stream first: it does not depend on x
+    RowLoads cur;
+    if (n < N) issue_row_loads(cur, wq + (size_t)n * K2, ws16 + (size_t)n * G, 0, lane, G);
+
     for (int idx = threadIdx.x; idx < MB * G; idx += GV_THREADS) {
         uint4 w = *reinterpret_cast<const uint4*>(xq + (size_t)idx * 4);
         uint4 e, o;
@@ -52,76 +87,43 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
     }
     __syncthreads();
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n_pairs = (N + 1) >> 1;
-    const size_t K2 = (size_t)K >> 1;
-
-    for (int pair = blockIdx.x * GV_WARPS + warp; pair < n_pairs; pair += gridDim.x * GV_WARPS) {
-        const int n0 = pair * 2;
-        const int n1 = min(n0 + 1, N - 1);
-        const uint8_t* w0 = wq + (size_t)n0 * K2;
-        const uint8_t* w1 = wq + (size_t)n1 * K2;
-        const unsigned short* s0 = reinterpret_cast<const unsigned short*>(ws) + (size_t)n0 * G;
-        const unsigned short* s1 = reinterpret_cast<const unsigned short*>(ws) + (size_t)n1 * G;
-        float acc0[MB], acc1[MB];
+    for (; n < N; n += stride) {
+        const uint8_t* wrow = wq + (size_t)n * K2;
+        const unsigned short* srow = ws16 + (size_t)n * G;
+        float acc[MB];
 #pragma unroll
-        for (int m = 0; m < MB; ++m) acc0[m] = acc1[m] = 0.f;
-
-        for (int gb = 0; gb < G; gb += 128) {               // 4 groups per lane per trip
-            uint4 wa[4], wb[4];
-            float sa[4], sb[4];
+        for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+        for (int gb = 0; gb < G; gb += 256) {
+            if (gb) issue_row_loads(cur, wrow, srow, gb, lane, G);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int g = gb + u * 32 + lane;
-                if (g < G) {
-                    wa[u] = ldg_nc_v4(w0 + (size_t)g * 16);
-                    wb[u] = ldg_nc_v4(w1 + (size_t)g * 16);
-                    sa[u] = bf16_bits_to_f32(__ldg(s0 + g));
-                    sb[u] = bf16_bits_to_f32(__ldg(s1 + g));
-                } else {
-                    wa[u] = wb[u] = make_uint4(0, 0, 0, 0);
-                    sa[u] = sb[u] = 0.f;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int g = min(gb + u * 32 + lane, G - 1);   // clamped lanes carry zero weights
-                uint4 ae, ao, be, bo;
-                unpack_x16(wa[u].x, ae.x, ao.x); unpack_x16(wa[u].y, ae.y, ao.y);
-                unpack_x16(wa[u].z, ae.z, ao.z); unpack_x16(wa[u].w, ae.w, ao.w);
-                unpack_x16(wb[u].x, be.x, bo.x); unpack_x16(wb[u].y, be.y, bo.y);
-                unpack_x16(wb[u].z, be.z, bo.z); unpack_x16(wb[u].w, be.w, bo.w);
+            for (int u = 0; u < 8; ++u) {
+                const int g = min(gb + u * 32 + lane, G - 1);          // lanes past the end carry zero weights
+                uint4 ae, ao;
+                unpack_x16(cur.w[u].x, ae.x, ao.x); unpack_x16(cur.w[u].y, ae.y, ao.y);
+                unpack_x16(cur.w[u].z, ae.z, ao.z); unpack_x16(cur.w[u].w, ae.w, ao.w);
+                const float sw = bf16_bits_to_f32(cur.s[u]);
 #pragma unroll
                 for (int m = 0; m < MB; ++m) {
                     const uint4 ve = xe[m * G + g], vo = xo[m * G + g];
-                    int d0 = dp4a_s8(ae.x, ve.x, 0); d0 = dp4a_s8(ao.x, vo.x, d0);
-                    d0 = dp4a_s8(ae.y, ve.y, d0); d0 = dp4a_s8(ao.y, vo.y, d0);
-                    d0 = dp4a_s8(ae.z, ve.z, d0); d0 = dp4a_s8(ao.z, vo.z, d0);
-                    d0 = dp4a_s8(ae.w, ve.w, d0); d0 = dp4a_s8(ao.w, vo.w, d0);
-                    int d1 = dp4a_s8(be.x, ve.x, 0); d1 = dp4a_s8(bo.x, vo.x, d1);
-                    d1 = dp4a_s8(be.y, ve.y, d1); d1 = dp4a_s8(bo.y, vo.y, d1);
-                    d1 = dp4a_s8(be.z, ve.z, d1); d1 = dp4a_s8(bo.z, vo.z, d1);
-                    d1 = dp4a_s8(be.w, ve.w, d1); d1 = dp4a_s8(bo.w, vo.w, d1);
-                    const float sx = sxf[m * G + g];
-                    acc0[m] = fmaf((float)d0, sx * sa[u], acc0[m]);
-                    acc1[m] = fmaf((float)d1, sx * sb[u], acc1[m]);
+                    int d = dp4a_s8(ae.x, ve.x, 0); d = dp4a_s8(ao.x, vo.x, d);
+                    d = dp4a_s8(ae.y, ve.y, d); d = dp4a_s8(ao.y, vo.y, d);
+                    d = dp4a_s8(ae.z, ve.z, d); d = dp4a_s8(ao.z, vo.z, d);
+                    d = dp4a_s8(ae.w, ve.w, d); d = dp4a_s8(ao.w, vo.w, d);
+                    acc[m] = fmaf((float)d, sxf[m * G + g] * sw, acc[m]);
                 }
             }
         }
+        // next row's first trip goes out before the reduction of this one
+        const int nn = n + stride;
+        if (nn < N) issue_row_loads(cur, wq + (size_t)nn * K2, ws16 + (size_t)nn * G, 0, lane, G);
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
 #pragma unroll
-            for (int off = 16; off; off >>= 1) {
-                acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], off);
-                acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], off);
-            }
+            for (int off = 16; off; off >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], off);
         }
         if (lane == 0) {
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
-                y[(size_t)m * N + n0] = __float2half_rn(acc0[m]);
-                if (n0 + 1 < N) y[(size_t)m * N + n0 + 1] = __float2half_rn(acc1[m]);
-            }
+            for (int m = 0; m < MB; ++m) y[(size_t)m * N + n] = __float2half_rn(acc[m]);
         }
     }
 }
@@ -133,12 +135,22 @@ static int launch_gemv(const uint8_t* xq, const void* xs, const uint8_t* wq, con
                        int64_t K, void* y, cudaStream_t st)
 {
     const size_t smem = gemv_smem_bytes(MB, K);
-    const int n_pairs = (int)((N + 1) / 2);
-    int ctas = (n_pairs + GV_WARPS - 1) / GV_WARPS;
-    const int resident = sm_count() * (smem > 64 * 1024 ? 1 : (smem > 24 * 1024 ? 2 : 4));
-    if (ctas > resident) ctas = resident;
-    gemv_dp4a_kernel<MB><<<ctas, GV_THREADS, smem, st>>>((const uint32_t*)xq, (const __nv_bfloat16*)xs, wq,
-                                                        (const __nv_bfloat16*)ws, (__half*)y, (int)N, (int)K);
+    // resident CTAs per SM for this shared-memory size (a host-side query, cached per size)
+    static thread_local size_t cached_smem = ~size_t(0);
+    static thread_local int cached_per_sm = 1;
+    if (cached_smem != smem) {
+        int q = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_dp4a_kernel<MB>, GV_THREADS, smem) != cudaSuccess || q < 1) q = 1;
+        cached_smem = smem;
+        cached_per_sm = q;
+    }
+    const int per_sm = cached_per_sm;
+    // persistent grid: every CTA resident at once, rows dealt round-robin to the warps
+    long long ctas = (long long)sm_count() * per_sm;
+    const long long needed = (N + GV_WARPS - 1) / GV_WARPS;
+    if (ctas > needed) ctas = needed;
+    gemv_dp4a_kernel<MB><<<(unsigned)ctas, GV_THREADS, smem, st>>>((const uint32_t*)xq, (const __nv_bfloat16*)xs, wq,
+                                                                   (const __nv_bfloat16*)ws, (__half*)y, (int)N, (int)K);
     return check_launch("gemv_dp4a");
 }
 

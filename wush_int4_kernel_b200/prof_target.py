@@ -1,0 +1,63 @@
+"""Minimal profiling target (the role of the reference's ``bench/prof_target.py``): runs one
+operator a few times on synthetic operands so that ``ncu -k regex:<kernel> -c <n>`` has a
+small, self-contained process to capture.
+
+    python -m wush_int4_kernel_b200.prof_target gemm  M N K [reps]
+    python -m wush_int4_kernel_b200.prof_target fused M K   [reps]
+    python -m wush_int4_kernel_b200.prof_target quant M K   [reps]
+
+Prints the mean time per call measured with CUDA events (never quote a time taken under a
+profiler).
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import _C, timing
+
+
+def _codes(rows, K, gen, dev):
+    q = torch.randint(0, 256, (rows, K // 2), generator=gen, device=dev, dtype=torch.uint8)
+    s = (0.01 * (1 + 0.5 * torch.rand(rows, K // 32, generator=gen, device=dev))).to(torch.bfloat16)
+    return q, s
+
+
+def main(argv):
+    op = argv[0]
+    dev = torch.device("cuda:0")
+    _C.init()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    if op == "gemm":
+        M, N, K = map(int, argv[1:4])
+        reps = int(argv[4]) if len(argv) > 4 else 5
+        xq, xs = _codes(M, K, gen, dev)
+        wq, ws = _codes(N, K, gen, dev)
+        if M == 1:
+            fn = lambda: _C.w4a4_gemv(xq, xs, wq, ws)
+        elif M <= 32:
+            fn = lambda: _C.w4a4_gemv_multi(xq, xs, wq, ws)
+        else:
+            fn = lambda: _C.w4a4_gemm_s4(xq, xs, wq, ws)
+        work = 2.0 * M * N * K
+    elif op in ("fused", "quant"):
+        M, K = map(int, argv[1:3])
+        reps = int(argv[3]) if len(argv) > 3 else 5
+        x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+        t = (torch.randn(K // 32, 32, 32, generator=gen, device=dev) / 6).to(torch.bfloat16)
+        fn = (lambda: _C.fused_transform_quant_int4_v3(x, t)) if op == "fused" else (lambda: _C.quant_int4(x))
+        work = 0.0
+    else:
+        raise SystemExit(__doc__)
+    for _ in range(3):
+        fn()
+    ms = timing.time_events(fn, reps) / reps
+    msg = f"{op} {' '.join(argv[1:])}: {ms * 1e3:.1f} us per call"
+    if work:
+        msg += f", {work / ms / 1e9:.1f} effective TOPS"
+    print(msg)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
