@@ -8,13 +8,17 @@
 // 9/16 byte per weight element out of HBM exactly once, at HBM rate, for 1..32 activation
 // rows; the arithmetic must fit in the shadow of that stream.
 //
-//   * The WEIGHTS are the wide MMA operand: a CTA owns 128 weight rows, each of its 8 compute
-//     warps 16 of them (the M=16 side of mma.m16n8k32.s8) against 1, 2 or 4 tiles of 8
-//     activation rows.
-//   * A ninth warp is the producer: per stage of 8 groups it issues four TMA tile loads
-//     (packed weight codes and activation codes with 128-byte swizzle, the two bf16 scale
-//     tiles) into a 4-deep ring; full/empty mbarriers, bounded waits.  Two CTAs fit per SM,
-//     so ~150 KB of loads are in flight per SM and the grid needs no persistence.
+//   * The WEIGHTS are the wide MMA operand: each compute warp owns 16 weight rows (the M=16
+//     side of mma.m16n8k32.s8) against 1, 2 or 4 tiles of 8 activation rows.  The number of
+//     compute warps per CTA (1..13) is chosen per call so that the whole grid is resident at
+//     once, two CTAs per SM, all with the same number of rows: one balanced wave.
+//   * One more warp is the producer: per stage of 4 groups it issues TMA tile loads of the
+//     packed weight and activation codes (64-byte swizzle) into a ring of up to 8 stages
+//     (~100 KB per CTA) and, with every even stage, the two bf16 scale tiles of 8 groups;
+//     full/empty mbarriers, bounded waits.
+//   * A further warp prepares the activations once per stage for everybody: nibbles widened
+//     into MMA-fragment order, bf16 scales converted to fp32 pairs (otherwise every compute
+//     warp would repeat that integer work, and the integer pipe is what limits this kernel).
 //   * ldmatrix on the swizzled tile hands every lane the one 4-byte word of 8 nibbles it
 //     needs per row (conflict free); one shift and two ANDs make two MMA registers of
 //     signed bytes (16 * code).  The k order inside a group is permuted identically for both
@@ -23,7 +27,8 @@
 //     1.5 * 2^23, so its int32 result read as fp32 is 12582912 + 256 * P_g, and
 //         t = fma(f, sw, -12582912 * sw)   (exact, = 256 * P_g * sw)
 //         acc = fma(t, sx, acc)
-//     applies both scales with two FMAs per output and group; 1/256 is applied once at the end.
+//     applies both scales with two FMAs per output and group (issued as packed fp32x2
+//     instructions on column pairs); 1/256 is applied once at the end.
 //
 // Algorithmic HBM bytes: 9*N*K/16 (weights) + 9*M*K/16 (activations, L2 resident) + 2*M*N.
 #include "common.cuh"
@@ -36,22 +41,43 @@ __device__ int g_device_flag;                       // library-owned error word 
 
 namespace {
 
-constexpr int ST_ROWS = 128, ST_KS = 8, ST_STAGES = 4;
-constexpr int ST_COMPUTE_WARPS = 8, ST_THREADS = (ST_COMPUTE_WARPS + 1) * 32;
+constexpr int ST_KS = 4;                            // groups per code stage (64 B of codes per row, 64-byte swizzle)
+constexpr int ST_SG = 8;                            // groups per scale tile (16 B per row): one per two code stages
+// compute warps per CTA (16 weight rows each): with two CTAs per SM, 13 + 1 warps leave 72
+// registers per thread, enough for one or two activation tiles; four tiles need ~100, so 9 + 1
+constexpr int max_warps(int mt) { return mt == 4 ? 9 : 13; }
+constexpr int ST_EXTRA_WARPS = 2;                   // TMA producer + activation prep
+constexpr int ST_MAX_STAGES = 8;
 constexpr uint32_t MAGIC_BITS = 0x4B400000u;
 constexpr float MAGIC = 12582912.0f;
 
-template <int MT>
-struct StreamSmem {
-    static constexpr int XROWS = MT * 8;
-    static constexpr int WC = 0;                                   // 128 rows x 128 B, swizzled
-    static constexpr int XC = WC + ST_ROWS * 128;                  // XROWS x 128 B, swizzled
-    static constexpr int WS = XC + 4096;                           // 128 rows x 8 bf16
-    static constexpr int XS = WS + ST_ROWS * 16;                   // XROWS x 8 bf16
-    static constexpr int STAGE = ((XS + XROWS * 16 + 1023) / 1024) * 1024;
-    static constexpr int TX = ST_ROWS * 128 + XROWS * 128 + ST_ROWS * 16 + XROWS * 16;
-    static constexpr int BARS = ST_STAGES * STAGE;
-    static constexpr int TOTAL = BARS + 2 * ST_STAGES * 8 + 1024;  // + alignment slack
+// Shared-memory plan of one CTA with `warps` compute warps (host and device agree on it):
+// a ring of code stages (weights + activations, 4 groups each) and a ring of scale slots
+// (8 groups each, filled together with every even code stage).  A scale slot is reused
+// `sslots` pairs later; sslots >= (stages + 1) / 2 makes the code ring's empty barriers
+// sufficient to protect it.
+struct StreamPlan {
+    int rows, xc, stage, stages, scales, sx, sslot, sslots, prep, pslot, pscale, bars, total, tx_codes, tx_scales;
+    __host__ __device__ StreamPlan(int warps, int xrows) {
+        rows = warps * 16;
+        xc = ((rows * 64 + 1023) / 1024) * 1024;             // activation codes after the weight codes
+        stage = xc + ((xrows * 64 + 1023) / 1024) * 1024;
+        sx = rows * 16;                                       // activation scales after the weight scales
+        sslot = ((sx + xrows * 16 + 127) / 128) * 128;
+        // per code stage, the activation tile once more in MMA-fragment order: [group][m-tile][lane]
+        // (b0, b1) words, then [group][m-tile][tig] fp32 scale pairs
+        pscale = ST_KS * (xrows / 8) * 32 * 8;
+        pslot = pscale + ST_KS * (xrows / 8) * 4 * 8;
+        stages = ST_MAX_STAGES;
+        while (stages > 2 && stages * (stage + pslot) + ((stages + 2) / 2) * sslot > 100 * 1024) --stages;   // two CTAs per SM
+        sslots = (stages + 2) / 2;
+        scales = stages * stage;
+        prep = scales + sslots * sslot;
+        bars = prep + stages * pslot;
+        total = bars + 3 * ST_MAX_STAGES * 8 + 1024;          // + slack for the 1 KB alignment
+        tx_codes = rows * 64 + xrows * 64;
+        tx_scales = rows * 16 + xrows * 16;
+    }
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* smem) {
@@ -69,139 +95,182 @@ __device__ __forceinline__ void mma_s8_biased(uint32_t (&d)[4], uint32_t a0, uin
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(MAGIC_BITS));
 }
 
-// bf16 element e (0..7) of a 16-byte vector of scales, as fp32
-__device__ __forceinline__ float scale_of(const uint4& v, int e) {
-    const uint32_t w = (e < 2) ? v.x : (e < 4) ? v.y : (e < 6) ? v.z : v.w;
+// bf16 element e (0..3) of an 8-byte vector of scales, as fp32
+__device__ __forceinline__ float scale_of(const uint2& v, int e) {
+    const uint32_t w = (e < 2) ? v.x : v.y;
     return (e & 1) ? bf16_hi(w) : bf16_lo(w);
 }
 
+// `warps` compute warps own 16 weight rows each; warp index `warps` is the TMA producer.
 template <int MT, bool PARTIALS>
-__global__ void __launch_bounds__(ST_THREADS, 2)
+__global__ void __launch_bounds__((max_warps(MT) + ST_EXTRA_WARPS) * 32, 2)
 w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_constant__ CUtensorMap map_xq,
                    const __grid_constant__ CUtensorMap map_ws, const __grid_constant__ CUtensorMap map_xs,
-                   __half* __restrict__ y, int32_t* __restrict__ part, int M, int N, int K)
+                   __half* __restrict__ y, int32_t* __restrict__ part, int M, int N, int K, int warps)
 {
-    using L = StreamSmem<MT>;
+    constexpr int XROWS = MT * 8;
+    const StreamPlan L(warps, XROWS);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BARS);
-    uint64_t* empty = full + ST_STAGES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+    uint64_t* empty = full + ST_MAX_STAGES;
+    uint64_t* xready = empty + ST_MAX_STAGES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = K >> 5, n_chunks = G / ST_KS;
-    const int n_base = blockIdx.x * ST_ROWS, m_base = blockIdx.y * L::XROWS;
+    const int n_base = blockIdx.x * L.rows, m_base = blockIdx.y * XROWS;
 
     if (tid == 0) {
-        for (int i = 0; i < ST_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], ST_COMPUTE_WARPS); }
+        for (int i = 0; i < L.stages; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], warps); tc::mbar_init(&xready[i], 1); }
         tc::mbar_fence_init();
     }
     __syncthreads();
 
-    if (warp == ST_COMPUTE_WARPS) {
+    if (warp == warps) {
         // ------------------------------ producer ----------------------------------------------
         if (lane == 0) {
             tc::prefetch_tensormap(&map_wq); tc::prefetch_tensormap(&map_xq);
             tc::prefetch_tensormap(&map_ws); tc::prefetch_tensormap(&map_xs);
-            uint32_t slot = 0, phase = 0;
-            int issued = 0;
+            int slot = 0, issued = 0;
+            uint32_t phase = 0;
             bool ok = true;
+            int sslot = 0;
             for (int kc = 0; kc < n_chunks; ++kc) {
                 if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
-                uint8_t* st = smem + slot * L::STAGE;
-                tc::mbar_expect_tx(&full[slot], L::TX);
-                tc::tma_load_2d(st + L::WC, &map_wq, &full[slot], kc * 128, n_base);
-                tc::tma_load_2d(st + L::XC, &map_xq, &full[slot], kc * 128, m_base);
-                tc::tma_load_2d(st + L::WS, &map_ws, &full[slot], kc * ST_KS, n_base);
-                tc::tma_load_2d(st + L::XS, &map_xs, &full[slot], kc * ST_KS, m_base);
+                uint8_t* st = smem + slot * L.stage;
+                const bool with_scales = (kc & 1) == 0;
+                tc::mbar_expect_tx(&full[slot], L.tx_codes + (with_scales ? L.tx_scales : 0));
+                tc::tma_load_2d(st, &map_wq, &full[slot], kc * 64, n_base);
+                tc::tma_load_2d(st + L.xc, &map_xq, &full[slot], kc * 64, m_base);
+                if (with_scales) {
+                    uint8_t* sc = smem + L.scales + sslot * L.sslot;
+                    tc::tma_load_2d(sc, &map_ws, &full[slot], (kc >> 1) * ST_SG, n_base);
+                    tc::tma_load_2d(sc + L.sx, &map_xs, &full[slot], (kc >> 1) * ST_SG, m_base);
+                    if (++sslot == L.sslots) sslot = 0;
+                }
                 ++issued;
-                if (++slot == ST_STAGES) { slot = 0; phase ^= 1; }
+                if (++slot == L.stages) { slot = 0; phase ^= 1; }
             }
             if (!ok) {
                 atomicExch(&g_device_flag, 1);
                 // copies already issued must land before the CTA's memory is given back
-                for (int i = 0; i < (issued < ST_STAGES ? issued : ST_STAGES); ++i)
+                for (int i = 0; i < (issued < L.stages ? issued : L.stages); ++i)
                     for (uint32_t spin = 0; spin < (1u << 16); ++spin)
                         if (tc::mbar_try_wait(&full[i], 0) || tc::mbar_try_wait(&full[i], 1)) break;
             }
         }
         return;
     }
+    if (warp == warps + 1) {
+        // ------------------------------ activation prep ------------------------------------------
+        // Every compute warp needs the same activation fragments and scales; this warp widens the
+        // nibbles and converts the bf16 scales ONCE per stage into MMA-fragment order so that the
+        // compute warps get them with two 8-byte shared loads per group and m-tile.
+        if constexpr (!PARTIALS) {
+            int slot = 0, sslot = 0;
+            uint32_t phase = 0;
+            for (int kc = 0; kc < n_chunks; ++kc) {
+                if (!tc::mbar_wait(&full[slot], phase)) { if (lane == 0) atomicExch(&g_device_flag, 3); return; }
+                const uint8_t* xc = smem + slot * L.stage + L.xc;
+                const uint8_t* sc = smem + L.scales + sslot * L.sslot + L.sx + (kc & 1) * 8;
+                uint2* frag = reinterpret_cast<uint2*>(smem + L.prep + slot * L.pslot);
+                float2* fsc = reinterpret_cast<float2*>(smem + L.prep + slot * L.pslot + L.pscale);
+#pragma unroll
+                for (int i = 0; i < ST_KS * MT; ++i) {                  // i = g * MT + mt
+                    const int g = i / MT, mt = i % MT;
+                    const int row = mt * 8 + (lane >> 2);
+                    const uint32_t w = *reinterpret_cast<const uint32_t*>(xc + row * 64 + ((g ^ ((row >> 1) & 3)) << 4) + (lane & 3) * 4);
+                    uint2 b;
+                    unpack_x16(w, b.x, b.y);
+                    frag[i * 32 + lane] = b;
+                }
+                for (int i = lane; i < ST_KS * MT * 4; i += 32) {        // i = (g * MT + mt) * 4 + tig
+                    const int t = i & 3, gm = i >> 2, g = gm / MT, mt = gm % MT;
+                    const unsigned short* r0 = reinterpret_cast<const unsigned short*>(sc + (mt * 8 + t * 2) * 16) + g;
+                    fsc[i] = make_float2(bf16_bits_to_f32(r0[0]), bf16_bits_to_f32(r0[8]));   // rows 2t and 2t+1 (16 B apart)
+                }
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&xready[slot]);
+                if (++slot == L.stages) { slot = 0; phase ^= 1; }
+                if ((kc & 1) && ++sslot == L.sslots) sslot = 0;
+            }
+        }
+        return;
+    }
+    if (warp > warps) return;
 
     // ---------------------------------- compute warps -------------------------------------------
     const int gid = lane >> 2, tig = lane & 3;
-    float acc[MT][4];
+    float2 acc[MT][2];                                   // [m-tile][row gid | row gid+8] x (col 2tig, 2tig+1)
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = make_float2(0.f, 0.f);
 
     // ldmatrix row addresses (the 128-byte swizzle XORs the 16-byte piece index with row & 7)
     const int w_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);        // matrices 0/2: rows 0-7, 1/3: rows 8-15
     const int w_gsel = lane >> 4;                                             // matrices 2,3 take the next group
-    uint32_t slot = 0, phase = 0;
+    const int swz = ((lane >> 1) & 3) << 4;             // 64-byte swizzle: piece index ^= (row >> 1) & 3
+    int slot = 0, sslot = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int kc = 0; kc < n_chunks; ++kc) {
         if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
-        const uint8_t* st = smem + slot * L::STAGE;
-        const uint8_t* wc = st + L::WC + w_row * 128;
-        const uint8_t* xc = st + L::XC;
-        // scales of the whole stage: 8 groups = one 16-byte vector per row
-        const uint4 swa = *reinterpret_cast<const uint4*>(st + L::WS + (warp * 16 + gid) * 16);
-        const uint4 swb = *reinterpret_cast<const uint4*>(st + L::WS + (warp * 16 + gid + 8) * 16);
-        uint4 sx0[MT], sx1[MT];
         if constexpr (!PARTIALS) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                sx0[mt] = *reinterpret_cast<const uint4*>(st + L::XS + (mt * 8 + tig * 2) * 16);
-                sx1[mt] = *reinterpret_cast<const uint4*>(st + L::XS + (mt * 8 + tig * 2 + 1) * 16);
-            }
+            if (!tc::mbar_wait(&xready[slot], phase)) { ok = false; break; }
         }
-#pragma unroll
-        for (int gq = 0; gq < ST_KS; gq += 4) {
-            // activation words for 4 groups: xb[group][m-tile]
-            uint32_t xb[4][MT];
-            if constexpr (MT == 4) {
-#pragma unroll
-                for (int gg = 0; gg < 4; ++gg) {
-                    uint32_t r[4];
-                    ldsm_x4(r, xc + lane * 128 + (((gq + gg) ^ (lane & 7)) << 4));
-#pragma unroll
-                    for (int mt = 0; mt < 4; ++mt) xb[gg][mt] = r[mt];
-                }
-            } else if constexpr (MT == 2) {
-#pragma unroll
-                for (int p = 0; p < 2; ++p) {
-                    uint32_t r[4];
-                    ldsm_x4(r, xc + (lane & 15) * 128 + (((gq + 2 * p + (lane >> 4)) ^ (lane & 7)) << 4));
-                    xb[2 * p][0] = r[0]; xb[2 * p][1] = r[1];
-                    xb[2 * p + 1][0] = r[2]; xb[2 * p + 1][1] = r[3];
-                }
-            } else {
-                uint32_t r[4];
-                ldsm_x4(r, xc + (lane & 7) * 128 + (((gq + (lane >> 3)) ^ (lane & 7)) << 4));
-#pragma unroll
-                for (int gg = 0; gg < 4; ++gg) xb[gg][0] = r[gg];
+        const uint8_t* st = smem + slot * L.stage;
+        const uint8_t* wc = st + w_row * 64;
+        const uint8_t* xc = st + L.xc;
+        const uint2* frag = reinterpret_cast<const uint2*>(smem + L.prep + slot * L.pslot) + lane;
+        const float2* fsc = reinterpret_cast<const float2*>(smem + L.prep + slot * L.pslot + L.pscale) + tig;
+        const uint8_t* sc = smem + L.scales + sslot * L.sslot + (kc & 1) * 8;   // second half of the 16-byte rows on odd stages
+        {
+            constexpr int gq = 0;
+            // scales of these four groups: one 8-byte vector per row
+            uint2 swa, swb;
+            if constexpr (!PARTIALS) {
+                swa = *reinterpret_cast<const uint2*>(sc + (warp * 16 + gid) * 16);
+                swb = *reinterpret_cast<const uint2*>(sc + (warp * 16 + gid + 8) * 16);
             }
 #pragma unroll
             for (int p = 0; p < 2; ++p) {
+                const int g0 = gq + 2 * p;                    // first group of the pair (compile-time)
                 uint32_t wa[4];
-                ldsm_x4(wa, wc + (((gq + 2 * p + w_gsel) ^ (lane & 7)) << 4));
+                ldsm_x4(wa, wc + (((g0 + w_gsel) << 4) ^ swz));
+                uint32_t xb[2][MT];                           // PARTIALS only: activation words straight from the tile
+                if constexpr (PARTIALS) {
 #pragma unroll
-                for (int gg2 = 0; gg2 < 2; ++gg2) {
-                    const int gl = gq + 2 * p + gg2;              // group inside the stage (compile-time)
+                    for (int gg = 0; gg < 2; ++gg) {
+                        uint32_t r[4];
+                        ldsm_x4(r, xc + lane * 64 + (((g0 + gg) << 4) ^ swz));
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) xb[gg][mt] = r[mt];
+                    }
+                }
+#pragma unroll
+                for (int gg = 0; gg < 2; ++gg) {
+                    const int e = 2 * p + gg;                 // group inside the quad (compile-time)
                     uint32_t a0, a1, a2, a3;
-                    unpack_x16(wa[gg2 * 2 + 0], a0, a2);          // row gid:     even codes, odd codes
-                    unpack_x16(wa[gg2 * 2 + 1], a1, a3);          // row gid + 8
-                    float s_a, s_b, c_a, c_b;
+                    unpack_x16(wa[gg * 2 + 0], a0, a2);       // row gid:     even codes, odd codes
+                    unpack_x16(wa[gg * 2 + 1], a1, a3);       // row gid + 8
+                    float2 s_a, s_b, c_a, c_b;
                     if constexpr (!PARTIALS) {
-                        s_a = scale_of(swa, gl); s_b = scale_of(swb, gl);
-                        c_a = -MAGIC * s_a; c_b = -MAGIC * s_b;   // exact: 2 x 8 significant bits
+                        const float fa = scale_of(swa, e), fb = scale_of(swb, e);
+                        s_a = make_float2(fa, fa); s_b = make_float2(fb, fb);
+                        c_a = make_float2(-MAGIC * fa, -MAGIC * fa);     // exact: 2 x 8 significant bits
+                        c_b = make_float2(-MAGIC * fb, -MAGIC * fb);
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         uint32_t b0, b1, d[4];
-                        unpack_x16(xb[2 * p + gg2][mt], b0, b1);
+                        if constexpr (PARTIALS) {
+                            unpack_x16(xb[gg][mt], b0, b1);
+                        } else {
+                            const uint2 b = frag[((gq + e) * MT + mt) * 32];
+                            b0 = b.x; b1 = b.y;
+                        }
                         mma_s8_biased(d, a0, a1, a2, a3, b0, b1);
                         if constexpr (PARTIALS) {
-                            const int g = kc * ST_KS + gl;
+                            const int g = kc * ST_KS + gq + e;
                             const int na = n_base + warp * 16 + gid, nb = na + 8;
                             const int m0 = m_base + mt * 8 + tig * 2, m1 = m0 + 1;
                             if (m0 < M && na < N) part[((size_t)m0 * N + na) * G + g] = (int32_t)(d[0] - MAGIC_BITS) >> 8;
@@ -209,11 +278,11 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
                             if (m0 < M && nb < N) part[((size_t)m0 * N + nb) * G + g] = (int32_t)(d[2] - MAGIC_BITS) >> 8;
                             if (m1 < M && nb < N) part[((size_t)m1 * N + nb) * G + g] = (int32_t)(d[3] - MAGIC_BITS) >> 8;
                         } else {
-                            const float x0 = scale_of(sx0[mt], gl), x1 = scale_of(sx1[mt], gl);
-                            acc[mt][0] = fmaf(fmaf(__uint_as_float(d[0]), s_a, c_a), x0, acc[mt][0]);
-                            acc[mt][1] = fmaf(fmaf(__uint_as_float(d[1]), s_a, c_a), x1, acc[mt][1]);
-                            acc[mt][2] = fmaf(fmaf(__uint_as_float(d[2]), s_b, c_b), x0, acc[mt][2]);
-                            acc[mt][3] = fmaf(fmaf(__uint_as_float(d[3]), s_b, c_b), x1, acc[mt][3]);
+                            const float2 x01 = fsc[((gq + e) * MT + mt) * 4];
+                            const float2 fa2 = make_float2(__uint_as_float(d[0]), __uint_as_float(d[1]));
+                            const float2 fb2 = make_float2(__uint_as_float(d[2]), __uint_as_float(d[3]));
+                            acc[mt][0] = __ffma2_rn(__ffma2_rn(fa2, s_a, c_a), x01, acc[mt][0]);
+                            acc[mt][1] = __ffma2_rn(__ffma2_rn(fb2, s_b, c_b), x01, acc[mt][1]);
                         }
                     }
                 }
@@ -221,7 +290,8 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
         }
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&empty[slot]);
-        if (++slot == ST_STAGES) { slot = 0; phase ^= 1; }
+        if (++slot == L.stages) { slot = 0; phase ^= 1; }
+        if ((kc & 1) && ++sslot == L.sslots) sslot = 0;
     }
     if (!ok) {
         if (lane == 0) atomicExch(&g_device_flag, 2);
@@ -233,35 +303,52 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             const int m0 = m_base + mt * 8 + tig * 2, m1 = m0 + 1;
-            if (m0 < M && na < N) y[(size_t)m0 * N + na] = __float2half_rn(acc[mt][0] * k);
-            if (m1 < M && na < N) y[(size_t)m1 * N + na] = __float2half_rn(acc[mt][1] * k);
-            if (m0 < M && nb < N) y[(size_t)m0 * N + nb] = __float2half_rn(acc[mt][2] * k);
-            if (m1 < M && nb < N) y[(size_t)m1 * N + nb] = __float2half_rn(acc[mt][3] * k);
+            if (m0 < M && na < N) y[(size_t)m0 * N + na] = __float2half_rn(acc[mt][0].x * k);
+            if (m1 < M && na < N) y[(size_t)m1 * N + na] = __float2half_rn(acc[mt][0].y * k);
+            if (m0 < M && nb < N) y[(size_t)m0 * N + nb] = __float2half_rn(acc[mt][1].x * k);
+            if (m1 < M && nb < N) y[(size_t)m1 * N + nb] = __float2half_rn(acc[mt][1].y * k);
         }
     }
+}
+
+// Compute warps per CTA: the rows are dealt so that ALL CTAs are resident at once (two per SM)
+// and carry the same number of 16-row blocks -- a second, partly filled wave would cost as much
+// as a full one because a CTA alone cannot pull more bandwidth than its pipeline depth allows.
+int pick_warps(int64_t N, int64_t m_blocks, int limit)
+{
+    const int64_t blocks = (N + 15) / 16;
+    int64_t slots = 2LL * sm_count() / (m_blocks > 0 ? m_blocks : 1);
+    if (slots < 1) slots = 1;
+    int64_t w = (blocks + slots - 1) / slots;
+    if (w > limit) w = limit;
+    if (w < 1) w = 1;
+    return (int)w;
 }
 
 template <int MT, bool PARTIALS>
 int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
                   void* y, int32_t* part, cudaStream_t st)
 {
-    using L = StreamSmem<MT>;
+    constexpr int XROWS = MT * 8;
+    const int64_t m_blocks = (M + XROWS - 1) / XROWS;
+    if (m_blocks > 65535) return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode): M too large");
+    const int warps = pick_warps(N, m_blocks, max_warps(MT));
+    const StreamPlan L(warps, XROWS);
     CUtensorMap mwq, mxq, mws, mxs;
     int s;
-    if ((s = make_map_2d(&mwq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 128, ST_ROWS, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
-    if ((s = make_map_2d(&mxq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, K / 2, M, 128, L::XROWS, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
-    if ((s = make_map_2d(&mws, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ws, K / 32, N, ST_KS, ST_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
-    if ((s = make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, K / 32, M, ST_KS, L::XROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
-    dim3 grid((unsigned)((N + ST_ROWS - 1) / ST_ROWS), (unsigned)((M + L::XROWS - 1) / L::XROWS));
-    if (grid.y > 65535) return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode): M too large");
-    w4a4_stream_kernel<MT, PARTIALS><<<grid, ST_THREADS, L::TOTAL, st>>>(mwq, mxq, mws, mxs, (__half*)y, part, (int)M,
-                                                                         (int)N, (int)K);
+    if ((s = make_map_2d(&mwq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 64, L.rows, CU_TENSOR_MAP_SWIZZLE_64B))) return s;
+    if ((s = make_map_2d(&mxq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, K / 2, M, 64, XROWS, CU_TENSOR_MAP_SWIZZLE_64B))) return s;
+    if ((s = make_map_2d(&mws, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ws, K / 32, N, ST_SG, L.rows, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
+    if ((s = make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, K / 32, M, ST_SG, XROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
+    dim3 grid((unsigned)((N + L.rows - 1) / L.rows), (unsigned)m_blocks);
+    w4a4_stream_kernel<MT, PARTIALS><<<grid, (warps + ST_EXTRA_WARPS) * 32, L.total, st>>>(mwq, mxq, mws, mxs, (__half*)y, part, (int)M,
+                                                                              (int)N, (int)K, warps);
     return check_launch("w4a4_stream");
 }
 
 template <int MT, bool P>
 cudaError_t set_attr() {
-    return cudaFuncSetAttribute(w4a4_stream_kernel<MT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, StreamSmem<MT>::TOTAL);
+    return cudaFuncSetAttribute(w4a4_stream_kernel<MT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
 }
 
 }  // namespace
