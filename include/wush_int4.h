@@ -89,16 +89,23 @@ int wush_fused_transform_quant_int4(const void* x, const void* t, int64_t rows, 
  * Replaces w4a4_gemm_s4 (csrc/gemm_s4.cu:320-379), w4a4_gemm / _v1 / _v2
  * (csrc/gemm_int4.cu:89-130, csrc/gemm_wmma.cu:128-172, csrc/gemm_wmma2.cu:141-181),
  * w4a4_gemv and w4a4_gemv_multi (csrc/gemv_int4.cu:145-223).
- *   WUSH_GEMM_AUTO   : pick by M (decode kernels for M <= 32, tile GEMM above)
- *   WUSH_GEMM_GEMV   : CUDA-core streaming kernel (M <= 4)
- *   WUSH_GEMM_DECODE : tensor-core streaming kernel, weights as the wide operand (M <= 32)
- *   WUSH_GEMM_TILE   : tiled tensor-core GEMM (any M)
- * K % 32 == 0.  `workspace` may be NULL when wush_w4a4_gemm_workspace_bytes() is 0. */
+ *   WUSH_GEMM_AUTO     : pick by M (GEMV for M <= 2, DECODE up to 32, TILE up to 127,
+ *                        TILE_F16 from 128)
+ *   WUSH_GEMM_GEMV     : CUDA-core streaming kernel (M <= 4)
+ *   WUSH_GEMM_DECODE   : tensor-core streaming kernel, weights as the wide operand (any M)
+ *   WUSH_GEMM_TILE     : tcgen05 kind::i8 tile GEMM, exact int32 sum per group (any M)
+ *   WUSH_GEMM_TILE_F16 : scales folded into exactly-representable fp16 operands, tcgen05
+ *                        kind::f16 with fp32 accumulation over the whole K (any M; the fast
+ *                        route for prefill; scratch = fp16 copies of both operands)
+ * K % 32 == 0.  Ask wush_w4a4_gemm_workspace_bytes() with the SAME variant for the scratch
+ * size; `workspace` may be NULL when it returns 0.  Word 0 of the scratch is an error word:
+ * non-zero after the call completes means a bounded wait inside the kernel gave up. */
 typedef enum {
     WUSH_GEMM_AUTO = 0,
     WUSH_GEMM_GEMV = 1,
     WUSH_GEMM_DECODE = 2,
-    WUSH_GEMM_TILE = 3
+    WUSH_GEMM_TILE = 3,
+    WUSH_GEMM_TILE_F16 = 4
 } wush_gemm_variant;
 size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
 int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws,

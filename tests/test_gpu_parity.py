@@ -192,6 +192,25 @@ def test_gemm_tile_tcgen05_vs_fp64(dev, orc, shape):
     _assert_close(y, y64, shape)
     y2 = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_DECODE)       # streaming kernel on the same data
     _assert_close(y2, y64, shape)
+    y3 = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_TILE_F16)     # scales folded into fp16 operands
+    _assert_close(y3, y64, shape)
+
+
+def test_f16_route_wide_scale_range(dev, orc):
+    """Rows whose group scales span many octaves (and exact-zero groups) through the fp16-folded route."""
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 160, 264, 512
+    X = (torch.randn(M, K, generator=g) * torch.exp2(torch.randint(-12, 8, (M, K // 32), generator=g).float()).repeat_interleave(32, 1))
+    W = (torch.randn(N, K, generator=g) * torch.exp2(torch.randint(-14, 2, (N, K // 32), generator=g).float()).repeat_interleave(32, 1))
+    X[3] = 0
+    W[:, 64:96] = 0
+    xq, xs = orc.quant_int4(orc.bits(X.to(torch.bfloat16)))
+    wq, ws = orc.quant_int4(orc.bits(W.to(torch.bfloat16)))
+    y64 = orc.gemm_f64(xq, xs, wq, ws)
+    y = cabi.gemm(*_to_dev(dev, xq, xs, wq, ws), variant=capi.GEMM_TILE_F16)
+    assert torch.isfinite(y.float()).all()
+    _assert_close(y, y64, "wide")
+    assert (y[3] == 0).all()
 
 
 SHAPES = [(64, 96, 128), (1, 64, 64), (300, 500, 512), (130, 512, 4096), (8, 4096, 4096),   # reference tests/test_p13.py:18

@@ -38,6 +38,7 @@ int gemv_set_attributes();
 int mma_set_attributes();
 int tc_set_attributes();
 int stream_set_attributes();
+int f16_set_attributes();
 
 static int init_device(int dev)
 {
@@ -52,6 +53,7 @@ static int init_device(int dev)
     if (int s = mma_set_attributes()) return s;
     if (int s = tc_set_attributes()) return s;
     if (int s = stream_set_attributes()) return s;
+    if (int s = f16_set_attributes()) return s;
     return WUSH_OK;
 }
 
@@ -86,17 +88,24 @@ bool tc_supported(int64_t M, int64_t N, int64_t K);
 size_t tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int tc_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
                 size_t, cudaStream_t);
+bool f16_supported(int64_t M, int64_t N, int64_t K);
+size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int f16_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
+                 size_t, cudaStream_t);
 
 // Which kernel a shape runs on.  GEMV: CUDA cores, M <= 4 (the exact per-group scaling costs
 // three instructions per (m, n, group), so beyond a few rows the dot products must move to
 // the tensor cores).  DECODE: weights-as-wide-operand tensor-core streaming, M <= 32.
-// TILE: tcgen05 tile GEMM for everything larger when the shape qualifies.
+// TILE: tcgen05 kind::i8 tile GEMM (exact integer group sums) for 32 < M < 128.
+// TILE_F16: scales folded into fp16 operands, tcgen05 kind::f16, for M >= 128 (several times
+// faster: no per-group epilogue; needs scratch for the fp16 operands).
 static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
 {
     if (variant != WUSH_GEMM_AUTO) return variant;
     const bool gemv_ok = gemv_smem_bytes((int)(M < 4 ? M : 4), K) <= 200 * 1024;
     if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0)) return WUSH_GEMM_GEMV;
     if (M <= 32) return WUSH_GEMM_DECODE;
+    if (M >= 128 && f16_supported(M, N, K)) return WUSH_GEMM_TILE_F16;
     return tc_supported(M, N, K) ? WUSH_GEMM_TILE : WUSH_GEMM_DECODE;
 }
 
@@ -113,7 +122,8 @@ WUSH_API size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, 
     using namespace wush;
     if (M <= 0 || N <= 0 || K <= 0 || K % 32) return 0;
     int v = resolve_variant(variant, M, N, K);
-    if (v == WUSH_GEMM_TILE && tc_supported(M, N, K)) return tc_workspace_bytes(M, N, K);
+    if (v == WUSH_GEMM_TILE_F16 && f16_supported(M, N, K)) return f16_workspace_bytes(M, N, K);
+    if ((v == WUSH_GEMM_TILE || v == WUSH_GEMM_TILE_F16) && tc_supported(M, N, K)) return tc_workspace_bytes(M, N, K);
     return 0;
 }
 
@@ -124,7 +134,7 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
     using namespace wush;
     if (int e = ensure_init()) return e;
     WUSH_REQUIRE(M >= 0 && N >= 0 && K > 0 && K % 32 == 0, "w4a4_gemm: K must be a positive multiple of 32");
-    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_TILE, "w4a4_gemm: unknown variant %d", variant);
+    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_TILE_F16, "w4a4_gemm: unknown variant %d", variant);
     if (M == 0 || N == 0) return WUSH_OK;
     WUSH_REQUIRE(xq && xs && wq && ws && y, "w4a4_gemm: null pointer");
     WUSH_REQUIRE(aligned16(xq) && aligned16(wq), "w4a4_gemm: packed codes must be 16-byte aligned");
@@ -139,6 +149,13 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
             return gemv_dispatch(xq, xs, wq, ws, M, N, K, y, st);
         case WUSH_GEMM_DECODE:
             return mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
+        case WUSH_GEMM_TILE_F16:
+            if (f16_supported(M, N, K)) {
+                if (!workspace) return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, none given",
+                                            f16_workspace_bytes(M, N, K));
+                return f16_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
+            }
+            // fall through: shapes the fp16 route does not take run on the exact tile kernel
         case WUSH_GEMM_TILE:
             if (!tc_supported(M, N, K)) return mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
             if (workspace_bytes < tc_workspace_bytes(M, N, K) || (tc_workspace_bytes(M, N, K) && !workspace))

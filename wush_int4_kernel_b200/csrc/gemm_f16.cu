@@ -1,0 +1,296 @@
+// Large-M product with the scales folded into fp16 operands (C-ABI wush_w4a4_gemm, variant
+// TILE_F16; what AUTO picks for M >= 128 when the caller provides the scratch).
+//
+//   Y[m][n] = sum_k (qa[m][k] * sx[m][g(k)]) * (qw[n][k] * sw[n][g(k)])
+//
+// Same contract as the reference's w4a4_gemm_s4 (csrc/gemm_s4.cu:320-379).  The exact
+// per-group route (gemm_tc.cu) must run two CUDA-core FMAs per output and group, which caps it
+// near 0.9 POPS on this part whatever the tensor cores do.  Here the per-group scales are
+// multiplied into the operands instead:
+//   * code * scale has at most 3 + 8 significant bits, so it is EXACTLY representable in fp16
+//     once each row is shifted by a power of two (2^-e, e = exponent of the row's largest
+//     scale; groups more than 2^13 below the row maximum lose low bits, a relative
+//     contribution < 1e-6);
+//   * products of two such values have <= 22 significant bits: exact in the tensor core's fp32
+//     accumulation, which then runs over the whole K without any per-group epilogue;
+//   * the two row shifts come back as one exact power-of-two factor in the epilogue.
+// Results agree with the fp64 arbiter to ~1e-6 before the fp16 output rounding; what this
+// route cannot do is expose the integer group sums (the i8 kernels do that).
+//
+// Two kernels:
+//   dequant_f16_kernel   one warp per row: codes + bf16 scales -> fp16 row (scratch) + 2^e
+//   gemm_f16_kernel      persistent 128 x 256 tiles: TMA (128-byte swizzle) -> 4-stage ring ->
+//                        tcgen05.mma kind::f16 (M=128, N=256, K=16) -> two TMEM accumulators in
+//                        rotation -> epilogue warps tcgen05.ld, scale by 2^(e_m+e_n), fp16 store
+// Algorithmic traffic: the pre-pass reads 9/16 B and writes 2 B per operand element; the GEMM
+// reads fp16 operands (L2-resident across the M tiles that share a weight tile).
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "tc_host.cuh"
+
+namespace wush {
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// pre-pass
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ s, __half* __restrict__ out,
+                   float* __restrict__ row_factor, long long rows, int K)
+{
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int G = K >> 5;
+    const unsigned short* sr = reinterpret_cast<const unsigned short*>(s) + row * G;
+    // largest scale of the row (bf16 bit patterns of non-negative values order like integers)
+    unsigned mx = 0;
+    for (int g = lane; g < G; g += 32) mx = max(mx, (unsigned)(sr[g] & 0x7fffu));
+#pragma unroll
+    for (int off = 16; off; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    int e = (int)(mx >> 7) - 127;                               // exponent of the largest scale
+    e = max(-100, min(100, e));
+    const float down = __uint_as_float((uint32_t)(127 - e) << 23);      // 2^-e
+    if (lane == 0) row_factor[row] = __uint_as_float((uint32_t)(127 + e) << 23);
+    const uint4* qr = reinterpret_cast<const uint4*>(q + row * (K >> 1));
+    uint4* orow = reinterpret_cast<uint4*>(out + row * K);
+    for (int g = lane; g < G; g += 32) {
+        const float sc = bf16_bits_to_f32(sr[g]) * down;        // exact: power-of-two shift
+        const uint4 w = qr[g];
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint4 o[4];
+        uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const int lo = ((int)(ww[i] << (28 - 8 * p))) >> 28;           // nibble 2p, sign extended
+                const int hi = ((int)(ww[i] << (24 - 8 * p))) >> 28;           // nibble 2p + 1
+                __half2 h = __floats2half2_rn((float)lo * sc, (float)hi * sc);  // exact products
+                ow[i * 4 + p] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) orow[g * 4 + i] = o[i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// GEMM
+// ------------------------------------------------------------------------------------------------
+constexpr int FM = 128, FN = 256, FK = 64;                     // tile; K elements per stage (128 B rows)
+constexpr int F_STAGES = 4, F_ACC = 2;
+constexpr int F_THREADS = 256;                                  // warp 0 TMA, warp 1 MMA, warps 4-7 epilogue
+constexpr int FA_BYTES = FM * 128, FB_BYTES = FN * 128;
+constexpr int F_STAGE = FA_BYTES + FB_BYTES;
+constexpr int F_BARS = F_STAGES * F_STAGE;
+constexpr int F_TOTAL = F_BARS + (2 * F_STAGES + 2 * F_ACC + 1) * 8 + 16 + 1024;
+
+// K-major operand in the 128-byte-swizzled layout TMA writes: rows of 128 B, 8-row groups 1 KB apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                                     // leading byte offset: unused with swizzle
+    d |= (uint64_t)(1024 >> 4) << 32;                           // stride byte offset between 8-row groups
+    d |= 1ull << 46;                                            // descriptor version of sm_100
+    d |= 2ull << 61;                                            // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(F_THREADS, 1)
+gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const float* __restrict__ fa, const float* __restrict__ fb, __half* __restrict__ y, int M, int N, int K,
+                int* __restrict__ err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + F_BARS);
+    uint64_t* empty = full + F_STAGES;
+    uint64_t* acc_full = empty + F_STAGES;
+    uint64_t* acc_empty = acc_full + F_ACC;
+    uint64_t* done_bar = acc_empty + F_ACC;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_m = (M + FM - 1) / FM, tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
+    const int k_steps = K / FK;
+
+    if (tid == 0) {
+        for (int i = 0; i < F_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
+        for (int i = 0; i < F_ACC; ++i) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 4); }
+        tc::mbar_init(done_bar, 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, 512);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(&map_b);
+            uint32_t slot = 0, phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
+                    uint8_t* st = smem + slot * F_STAGE;
+                    tc::mbar_expect_tx(&full[slot], F_STAGE);
+                    tc::tma_load_2d(st, &map_a, &full[slot], ks * FK, m0);
+                    tc::tma_load_2d(st + FA_BYTES, &map_b, &full[slot], ks * FK, n0);
+                    ++issued;
+                    if (++slot == F_STAGES) { slot = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                atomicExch(err, 1);
+                for (int i = 0; i < (issued < F_STAGES ? issued : F_STAGES); ++i)
+                    for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                        if (tc::mbar_try_wait(&full[i], 0) || tc::mbar_try_wait(&full[i], 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 0, ab = 0, aphase = 0;
+            const uint32_t idesc = tc::idesc_f16(FN);
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (!tc::mbar_wait(&acc_empty[ab], aphase ^ 1)) { ok = false; break; }
+                tc::tc_fence_after();
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
+                    tc::tc_fence_after();
+                    const uint32_t sa = tc::smem_u32(smem + slot * F_STAGE), sb = sa + FA_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < FK / 16; ++kk)                       // 32 bytes further along K inside the swizzled row
+                        mma_f16(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
+                                (ks | kk) ? 1u : 0u);
+                    tc::mma_commit(&empty[slot]);                              // stage free once these MMAs retire
+                    if (++slot == F_STAGES) { slot = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc::mma_commit(&acc_full[ab]);
+                if (++ab == F_ACC) { ab = 0; aphase ^= 1; }
+            }
+            if (!ok) atomicExch(err, 2);
+            tc::mma_commit(done_bar);
+            for (uint32_t spin = 0; spin < WUSH_SPIN_LIMIT; ++spin)
+                if (tc::mbar_try_wait(done_bar, 0)) break;
+        }
+    } else if (warp >= 4) {
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        uint32_t ab = 0, aphase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
+            if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
+            tc::tc_fence_after();
+            const int m = m0 + row;
+            const float fm = (m < M) ? fa[m] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < FN / 32; ++c) {
+                uint32_t v[32];
+                tc::tmem_ld32(tmem + lane_base + ab * FN + c * 32, v);
+                tc::tmem_ld_wait();
+                if (c == FN / 32 - 1) {                        // accumulator fully read: hand it back
+                    tc::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive(&acc_empty[ab]);
+                }
+                const int n = n0 + c * 32;
+                if (m < M && n < N) {
+                    __half* yr = y + (size_t)m * N + n;
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        if (n + v8 * 8 + 8 <= N) {
+                            const float4 f0 = *reinterpret_cast<const float4*>(fb + n + v8 * 8);
+                            const float4 f1 = *reinterpret_cast<const float4*>(fb + n + v8 * 8 + 4);
+                            const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                            uint32_t o[4];
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
+                                                              __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
+                                o[p] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                }
+            }
+            if (++ab == F_ACC) { ab = 0; aphase ^= 1; }
+        }
+        if (!ok && lane == 0) atomicExch(err, 4);
+    }
+
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem, 512);
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+
+int f16_set_attributes()
+{
+    if (int s = resolve_tensor_map_encoder()) return s;
+    cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "f16 GEMM: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    return WUSH_OK;
+}
+
+// K in whole 64-element stages, 16-byte output vectors and factor vectors.
+bool f16_supported(int64_t M, int64_t N, int64_t K) { return M >= 1 && K % 64 == 0 && N % 8 == 0; }
+
+// scratch: error word | fp16 activations (M x K) | fp16 weights (N x K) | 2^e per row of each
+size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    return 256 + align256((size_t)M * K * 2) + align256((size_t)N * K * 2) + align256((size_t)M * 4) + align256((size_t)N * 4);
+}
+
+int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
+                 void* y, void* workspace, size_t workspace_bytes, cudaStream_t st)
+{
+    if (!aligned16(y) || !aligned16(workspace))
+        return fail(WUSH_ERR_INVALID_ARGUMENT, "w4a4_gemm(f16): output and workspace must be 16-byte aligned");
+    if (workspace_bytes < f16_workspace_bytes(M, N, K))
+        return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, %zu given",
+                    f16_workspace_bytes(M, N, K), workspace_bytes);
+    uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+    int* err = reinterpret_cast<int*>(base);
+    __half* a16 = reinterpret_cast<__half*>(base + 256);
+    __half* b16 = reinterpret_cast<__half*>(base + 256 + align256((size_t)M * K * 2));
+    float* fa = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(b16) + align256((size_t)N * K * 2));
+    float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
+    cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    dequant_f16_kernel<<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
+    dequant_f16_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
+    if (int s = check_launch("dequant_f16")) return s;
+    CUtensorMap ma, mb;
+    int s;
+    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, FK, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b16, K, N, FK, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    const int64_t tiles = ((M + FM - 1) / FM) * ((N + FN - 1) / FN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    gemm_f16_kernel<<<grid, F_THREADS, F_TOTAL, st>>>(ma, mb, fa, fb, (__half*)y, (int)M, (int)N, (int)K, err);
+    return check_launch("gemm_f16");
+}
+
+}  // namespace wush
