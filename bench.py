@@ -35,8 +35,8 @@ sys.path.insert(0, ROOT)
 K_DIM, N_DIM = 8192, 57344
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the product kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists).
-PRODUCT_KERNEL_DRAM_BYTES = None
+# capture summarised in profiles/gemv_dp4a_decode_m1_k8192_n57344.md (264.29 MB read + 3.66 MB written).
+PRODUCT_KERNEL_DRAM_BYTES = 267_945_472
 
 
 def algorithmic_bytes_product(M: int, N: int, K: int) -> int:
@@ -222,7 +222,7 @@ def run_gpu_arm(args):
     peak, peak_kind = measured_hbm_peak()
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": PRODUCT_KERNEL_DRAM_BYTES, "peak_kind": f"of {peak_kind}", "kernel": "w4a4 product",
+                "traffic": (PRODUCT_KERNEL_DRAM_BYTES * n_local // N_DIM) if M == 1 else None, "peak_kind": f"of {peak_kind}", "kernel": "w4a4 product",
                 "kernel_us": kernel_ms * 1e3, "algorithmic_bytes": alg_bytes}
 
     # ---- end to end through the public ops: host activations in, host result out -------------
