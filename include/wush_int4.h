@@ -112,6 +112,29 @@ int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const v
                    int64_t M, int64_t N, int64_t K, void* y, int variant, void* workspace,
                    size_t workspace_bytes, void* stream);
 
+/* --- product without caller scratch (no counterpart in the reference) -----------------------
+ * For hosts that cannot hand this library any scratch and may not allocate device memory
+ * themselves once they are running: servers that size a single arena at start-up and forbid
+ * cudaMalloc afterwards, processes held to a fixed device-memory budget, control loops that
+ * cannot tolerate the implicit synchronisation of an allocation.  Same result as
+ * wush_w4a4_gemm(..., WUSH_GEMM_TILE_F16, ...), but the scratch is an array of
+ * WUSH_STATIC_SCRATCH_BYTES that is part of the library image: every GPU that loads the library
+ * keeps it until the process exits, so the limit is deliberately modest.
+ *   - Shapes whose scratch (about 2*(M+N)*K bytes) exceeds the limit are refused with
+ *     WUSH_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
+ *   - Neither this call nor anything it uses calls cudaMalloc / cudaFree or an allocating
+ *     library routine.
+ *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress
+ *     with that device current); make that first call before any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents; the library
+ *     re-initialises what it needs, but two calls that overlap on the GPU (different streams,
+ *     no dependency between them) race on it.  Serialise them. */
+#define WUSH_STATIC_SCRATCH_BYTES (32u << 20)
+size_t wush_w4a4_gemm_static_scratch_limit(void);
+int wush_w4a4_gemm_static_scratch(const uint8_t* xq, const void* xs, const uint8_t* wq,
+                                  const void* ws, int64_t M, int64_t N, int64_t K, void* y,
+                                  void* stream);
+
 /* --- a11: tensor-core self-tests ------------------------------------------------------
  * wush_i8_atom_selftest replaces s4_atom_selftest (csrc/gemm_s4.cu:50-82):
  * a (8,32) int8 in [-8,7], b (32,8) int8 -> c (8,8) int32 through one int8 MMA atom.

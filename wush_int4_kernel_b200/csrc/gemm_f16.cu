@@ -24,6 +24,8 @@
 //                        rotation -> epilogue warps tcgen05.ld, scale by 2^(e_m+e_n), fp16 store
 // Algorithmic traffic: the pre-pass reads 9/16 B and writes 2 B per operand element; the GEMM
 // reads fp16 operands (L2-resident across the M tiles that share a weight tile).
+#include <mutex>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tc_host.cuh"
@@ -294,3 +296,74 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
 }
 
 }  // namespace wush
+
+// ------------------------------------------------------------------------------------------------
+// Variant for callers that may not allocate device memory
+// ------------------------------------------------------------------------------------------------
+// Some hosts give a plugin no way to obtain scratch: an inference server that sizes one arena at
+// start-up and forbids cudaMalloc afterwards, a process confined to a fixed memory budget, or a
+// latency-critical loop that cannot afford cudaMalloc's implicit device synchronisation.  For
+// them the scratch of the fp16-folded product lives in this translation unit as a fixed array in
+// device memory.  Every GPU that loads the library holds these WUSH_STATIC_SCRATCH_BYTES until the
+// process exits, which is why the limit is modest.
+//
+// `g_static_scratch` names the array for DEVICE code; on the host the same identifier is only a
+// handle, not an address.  The address a kernel can use is obtained once per device with
+// cudaGetSymbolAddress (that device being current) and cached.
+namespace wush {
+namespace {
+
+__device__ __align__(256) uint8_t g_static_scratch[WUSH_STATIC_SCRATCH_BYTES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+void* g_static_ptr[STATIC_MAX_DEVICES];          // device address of the array, per device (null = not resolved yet)
+std::mutex g_static_mutex;
+
+int static_scratch_pointer(void** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) return fail(WUSH_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);          // resolves the array on the CURRENT device
+        if (e != cudaSuccess || !p)
+            return fail(WUSH_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return WUSH_OK;
+}
+
+}  // namespace
+}  // namespace wush
+
+WUSH_API size_t wush_w4a4_gemm_static_scratch_limit(void) { return WUSH_STATIC_SCRATCH_BYTES; }
+
+WUSH_API int wush_w4a4_gemm_static_scratch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M,
+                                           int64_t N, int64_t K, void* y, void* stream)
+{
+    using namespace wush;
+    if (int e = ensure_init()) return e;
+    WUSH_REQUIRE(M >= 0 && N >= 0 && K > 0, "w4a4_gemm_static_scratch: bad shape");
+    if (M == 0 || N == 0) return WUSH_OK;
+    WUSH_REQUIRE(xq && xs && wq && ws && y, "w4a4_gemm_static_scratch: null pointer");
+    WUSH_REQUIRE(aligned16(xq) && aligned16(wq), "w4a4_gemm_static_scratch: packed codes must be 16-byte aligned");
+    if (!f16_supported(M, N, K))
+        return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm_static_scratch: needs K %% 64 == 0 and N %% 8 == 0 (got K=%lld, N=%lld)",
+                    (long long)K, (long long)N);
+    const size_t need = f16_workspace_bytes(M, N, K);
+    if (need > (size_t)WUSH_STATIC_SCRATCH_BYTES)
+        return fail(WUSH_ERR_WORKSPACE,
+                    "w4a4_gemm_static_scratch: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in array holds %zu; "
+                    "use wush_w4a4_gemm with caller-provided scratch",
+                    (long long)M, (long long)N, (long long)K, need, (size_t)WUSH_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int e = static_scratch_pointer(&scratch)) return e;
+    // f16_dispatch zeroes the error word at the head of the scratch on the stream; every other
+    // byte it reads is written first by its own pre-pass, so stale contents of an earlier call
+    // are never consumed.
+    return f16_dispatch(xq, xs, wq, ws, M, N, K, y, scratch, (size_t)WUSH_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+}
