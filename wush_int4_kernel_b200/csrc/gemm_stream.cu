@@ -43,9 +43,8 @@ namespace {
 
 constexpr int ST_KS = 4;                            // groups per code stage (64 B of codes per row, 64-byte swizzle)
 constexpr int ST_SG = 8;                            // groups per scale tile (16 B per row): one per two code stages
-// compute warps per CTA (16 weight rows each): with two CTAs per SM, 13 + 1 warps leave 72
-// registers per thread, enough for one or two activation tiles; four tiles need ~100, so 9 + 1
-constexpr int max_warps(int mt) { return mt == 4 ? 9 : 13; }
+// compute warps per CTA (16 weight rows each): 13 + 2 warps, two CTAs per SM, 64 registers per thread
+constexpr int max_warps(int) { return 13; }
 constexpr int ST_EXTRA_WARPS = 2;                   // TMA producer + activation prep
 constexpr int ST_MAX_STAGES = 8;
 constexpr uint32_t MAGIC_BITS = 0x4B400000u;
