@@ -83,6 +83,14 @@ typedef enum { WUSH_TQ_EXACT = 0, WUSH_TQ_FAST = 1 } wush_tq_variant;
 int wush_fused_transform_quant_int4(const void* x, const void* t, int64_t rows, int64_t K,
                                     int variant, uint8_t* q, void* s, void* stream);
 
+/* The same op (FAST arithmetic) fed by the fp16 output of a fused gate+up projection:
+ *   h = bf16( SiLU(gate) * up ) in fp32, gate = gate_up[:, :K], up = gate_up[:, K:],
+ * then the transform + quantisation of h.  No counterpart in the reference, whose FFN callers
+ * compute h with separate torch kernels between the two projections.
+ * gate_up: rows*2K fp16;  t: (K/32)*1024 bf16;  q: rows*K/2;  s: rows*K/32 bf16. */
+int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t, int64_t rows,
+                                             int64_t K, uint8_t* q, void* s, void* stream);
+
 /* --- a8..a10: group-scaled W4A4 product ---------------------------------------------
  * Y[m][n] = sum_g sx[m][g] * sw[n][g] * P_g,  P_g = sum_{k in g} qa*qw exact in int32,
  * fp32 accumulation over groups, fp16 output.

@@ -1,0 +1,120 @@
+"""GPU tests of the layer level: M-dispatch, column / row parallel shards and the FFN block.
+
+The reference has no multi-GPU code, so the sharded results are pinned as compositions of the
+single-op semantics: shards computed one after the other on ONE GPU must reproduce the
+unsharded layer (column parallel: bit for bit; row parallel: to fp32 summation order)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def setup():
+    assert torch.cuda.is_available()
+    from my_int4 import _C
+    from wush_int4_kernel_b200 import synth
+    _C.init()
+    layer = synth.make_layer(1024, 768, seed=3, device="cuda", quantiser=_C.quant_int4)
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    return _C, synth, layer, gen
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 32, 40, 200])
+def test_layer_dispatch_matches_oracle(setup, orc, M):
+    _C, synth, layer, gen = setup
+    from wush_int4_kernel_b200.linear import W4A4Linear
+    lin = W4A4Linear(layer.t_bf16, layer.wq, layer.ws)
+    x = synth.draw_activations(M, 1024, layer.outliers, gen)
+    y = lin(x)
+    assert y.shape == (M, 768) and y.dtype == torch.float16
+    xq, xs = _C.fused_transform_quant_int4_v3(x, layer.t_bf16) if M > 32 else _C.fused_transform_quant_int4_smallm(x, layer.t_bf16)
+    y64 = orc.gemm_f64(xq.cpu().numpy(), orc.bits(xs), layer.wq.cpu().numpy(), orc.bits(layer.ws))
+    rel = np.linalg.norm(y.double().cpu().numpy() - y64) / np.linalg.norm(y64)
+    assert rel <= 1e-3, rel
+    y3 = lin(x.reshape(1, M, 1024))
+    assert y3.shape == (1, M, 768) and torch.equal(y3[0], y)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_column_parallel_shards_compose(setup, world):
+    _C, synth, layer, gen = setup
+    from wush_int4_kernel_b200.linear import ColumnParallelW4A4Linear, W4A4Linear
+    x = synth.draw_activations(3, 1024, layer.outliers, gen)
+    full = W4A4Linear(layer.t_bf16, layer.wq, layer.ws)(x)
+    parts = [ColumnParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, r, multiple=32)(x) for r in range(world)]
+    assert sum(p.shape[1] for p in parts) == 768
+    assert torch.equal(torch.cat(parts, dim=1), full)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_row_parallel_partials_sum(setup, orc, world):
+    _C, synth, layer, gen = setup
+    from wush_int4_kernel_b200.linear import RowParallelW4A4Linear, W4A4Linear, shard_bounds
+    x = synth.draw_activations(40, 1024, layer.outliers, gen)
+    full = W4A4Linear(layer.t_bf16, layer.wq, layer.ws)(x).float()
+    acc = torch.zeros_like(full)
+    for r in range(world):
+        shard = RowParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, r, reduce_output=False)
+        k0, k1 = shard_bounds(1024, world, r, 32)
+        acc += shard(x[:, k0:k1].contiguous()).float()
+    rel = ((acc - full).norm() / full.norm()).item()
+    assert rel <= 2e-3, rel            # each partial is rounded to fp16 before the sum
+
+
+def test_ffn_block_single_rank_equals_composition(setup):
+    _C, synth, layer, gen = setup
+    from wush_int4_kernel_b200.linear import TensorParallelFFN, W4A4Linear
+    hidden, inter = 512, 1024
+    gu = synth.make_layer(hidden, 2 * inter, seed=7, device="cuda", quantiser=_C.quant_int4)
+    dn = synth.make_layer(inter, hidden, seed=8, device="cuda", quantiser=_C.quant_int4)
+    ffn = TensorParallelFFN((gu.t_bf16, gu.wq, gu.ws), (dn.t_bf16, dn.wq, dn.ws), world=1, rank=0)
+    x = synth.draw_activations(24, hidden, gu.outliers, gen)
+    y = ffn(x)
+    assert torch.equal(y, ffn.reference_call(x))          # fused activation kernel == separate torch kernels, bit for bit
+    g = W4A4Linear(gu.t_bf16, gu.wq, gu.ws)(x)
+    h = (torch.nn.functional.silu(g[:, :inter].float()) * g[:, inter:].float()).to(torch.bfloat16)
+    expect = W4A4Linear(dn.t_bf16, dn.wq, dn.ws)(h)
+    assert y.shape == (24, hidden) and torch.equal(y, expect)
+    # two ranks' worth of shards, run one after the other: partial products add up to the block
+    parts = []
+    for r in range(2):
+        shard = TensorParallelFFN((gu.t_bf16, gu.wq, gu.ws), (dn.t_bf16, dn.wq, dn.ws), world=2, rank=r)
+        shard.down.reduce_output = False
+        parts.append(shard(x).float())
+    rel = ((parts[0] + parts[1] - expect.float()).norm() / expect.float().norm()).item()
+    assert rel <= 5e-3, rel
+
+
+def test_two_process_nccl_if_available():
+    """torchrun with two ranks when the box has two GPUs: column-parallel all-gather and
+    row-parallel all-reduce against the unsharded layer (skipped on single-GPU boxes)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29533", os.path.join(root, "tests", "nccl_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "rank 0 ok" in out.stdout and "rank 1 ok" in out.stdout
+
+
+@pytest.mark.parametrize("rows,K", [(1, 256), (7, 1024), (33, 512), (300, 2048)])
+def test_fused_silu_mul_transform_quant(setup, rows, K):
+    """One kernel for SiLU(gate) * up -> bf16 -> transform -> quantise against the composition
+    `fused_transform_quant_int4_v3((silu(gate.float()) * up.float()).bfloat16(), t)`."""
+    _C, synth, layer, gen = setup
+    gate_up = (2.0 * torch.randn(rows, 2 * K, generator=gen, device="cuda")).to(torch.float16)
+    t = (torch.randn(K // 32, 32, 32, generator=gen, device="cuda") / 6).to(torch.bfloat16)
+    q, s = _C.fused_silu_mul_transform_quant_int4(gate_up, t)
+    h = (torch.nn.functional.silu(gate_up[:, :K].float()) * gate_up[:, K:].float()).to(torch.bfloat16).contiguous()
+    q_ref, s_ref = _C.fused_transform_quant_int4_v3(h, t)
+    assert q.shape == (rows, K // 2) and s.shape == (rows, K // 32) and s.dtype == torch.bfloat16
+    assert torch.equal(s, s_ref) and torch.equal(q, q_ref)
+    with pytest.raises(RuntimeError):
+        _C.fused_silu_mul_transform_quant_int4(gate_up.float(), t)

@@ -70,6 +70,27 @@ std::vector<torch::Tensor> fused_transform_quant_int4(torch::Tensor x, torch::Te
 {
     return fused_tq(x, t, WUSH_TQ_EXACT, "fused_transform_quant_int4");
 }
+// Addition to the reference surface: SiLU(gate) * up -> bf16 -> transform -> quantise in one pass
+// over the fp16 output of a fused gate+up projection (gate half first).
+std::vector<torch::Tensor> fused_silu_mul_transform_quant_int4(torch::Tensor gate_up, torch::Tensor t)
+{
+    TORCH_CHECK(gate_up.is_cuda() && gate_up.is_contiguous() && t.is_cuda() && t.is_contiguous(),
+                "gate_up/t must be contiguous CUDA tensors");
+    TORCH_CHECK(gate_up.scalar_type() == torch::kHalf && t.scalar_type() == torch::kBFloat16,
+                "gate_up must be fp16, t bf16");
+    TORCH_CHECK(gate_up.dim() >= 1 && t.dim() == 3 && gate_up.size(-1) % 64 == 0, "gate_up must be (..., 2K), K % 32 == 0");
+    const int64_t K = gate_up.size(-1) / 2, C = K / 32;
+    TORCH_CHECK(t.size(0) == C && t.size(1) == 32 && t.size(2) == 32, "T must be (K/32, 32, 32)");
+    TORCH_CHECK(gate_up.device() == t.device(), "gate_up and t must be on the same device");
+    const at::cuda::OptionalCUDAGuard guard(gate_up.device());
+    const int64_t rows = gate_up.numel() / (2 * K);
+    auto q = torch::empty(with_last(gate_up, K / 2), gate_up.options().dtype(torch::kUInt8));
+    auto s = torch::empty(with_last(gate_up, C), gate_up.options().dtype(torch::kBFloat16));
+    check_status(wush_fused_silu_mul_transform_quant_int4(gate_up.data_ptr(), t.data_ptr(), rows, K, q.data_ptr<uint8_t>(),
+                                                          s.data_ptr(), stream_of(gate_up)),
+                 "fused_silu_mul_transform_quant_int4");
+    return {q, s};
+}
 std::vector<torch::Tensor> fused_transform_quant_int4_wmma(torch::Tensor x, torch::Tensor t)
 {
     return fused_tq(x, t, WUSH_TQ_FAST, "fused_transform_quant_int4_wmma");
@@ -279,6 +300,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
           py::arg("x"), py::arg("t"));
     m.def("fused_transform_quant_int4_smallm", &fused_transform_quant_int4_smallm,
           "Fused WUSH transform + INT4 quantise (decode shapes)", py::arg("x"), py::arg("t"));
+    m.def("fused_silu_mul_transform_quant_int4", &fused_silu_mul_transform_quant_int4,
+          "SiLU(gate) * up -> bf16 -> WUSH transform + INT4 quantise, from the fp16 (..., 2K) gate+up output",
+          py::arg("gate_up"), py::arg("t"));
     m.def("fused_transform_quant_int4", &fused_transform_quant_int4,
           "Fused WUSH transform + INT4 quantise (bit-exact serial arithmetic)", py::arg("x"), py::arg("t"));
     m.def("w4a4_gemm_v2", &w4a4_gemm_v2, "W4A4 group-scaled product (alias of the current kernels)", py::arg("xq"),

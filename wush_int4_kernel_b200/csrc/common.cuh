@@ -105,4 +105,32 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
     return v;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// A producer calls pdl_launch_dependents() once its CTAs are resident; a consumer launched with
+// launch_dependent() may then start, but sees the producer's writes only after pdl_wait(), which
+// returns when the producer grid has finished and flushed.  Before the wait a consumer may only
+// touch data in ways that cannot observe a stale value (here: L2 prefetches).  Both calls are
+// no-ops when the neighbouring kernel does not take part.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Launch with the programmatic-stream-serialisation attribute (host side).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace wush

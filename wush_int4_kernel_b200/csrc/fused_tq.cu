@@ -117,11 +117,38 @@ __device__ __forceinline__ void quantise_row_octet(const float (&v)[8], uint32_t
     *word = w;
 }
 
+// SiLU(gate) * up of 8 fp16 pairs -> 8 bf16 in one 16-byte register set.  fp32 throughout:
+// s = g / (1 + exp(-g)), h = bf16(s * u) -- what `(silu(gate.float()) * up.float()).bfloat16()`
+// computes, the rounding of h to bf16 being forced by the transform op's input type.
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g2, uint32_t u2) {
+    const float2 g = __half22float2(*reinterpret_cast<const __half2*>(&g2));
+    const float2 u = __half22float2(*reinterpret_cast<const __half2*>(&u2));
+    const float a = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, expf(-g.x))), u.x);
+    const float b = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, expf(-g.y))), u.y);
+    return f32_to_bf16_bits(a) | (f32_to_bf16_bits(b) << 16);
+}
+
+// 8 consecutive inputs of row r for this lane.  SILU: `x` is the fp16 output of a fused gate+up
+// projection, (rows, 2K) with the gate half first; the activation is computed on the fly.
+template <bool SILU>
+__device__ __forceinline__ uint4 load_octet(const void* x, long long r, int C, int g, int tig) {
+    if constexpr (!SILU) {
+        return ldg_nc_v4(reinterpret_cast<const __nv_bfloat16*>(x) + ((size_t)r * C + g) * 32 + tig * 8);
+    } else {
+        const __half* gate = reinterpret_cast<const __half*>(x) + ((size_t)r * 2 * C + g) * 32 + tig * 8;
+        const uint4 gv = ldg_nc_v4(gate), uv = ldg_nc_v4(gate + (size_t)C * 32);
+        return make_uint4(silu_mul_pair(gv.x, uv.x), silu_mul_pair(gv.y, uv.y), silu_mul_pair(gv.z, uv.z),
+                          silu_mul_pair(gv.w, uv.w));
+    }
+}
+
+template <bool SILU>
 __global__ void __launch_bounds__(256)
-fused_tq_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ t,
+fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ t,
                      uint32_t* __restrict__ q_out,        // rows * C * 4 words
                      __nv_bfloat16* __restrict__ s_out, long long rows, int C, int rows_per_cta)
 {
+    pdl_launch_dependents();                              // the consumer may get resident; it waits before reading q/s
     const int warps = blockDim.x >> 5;
     const int g = blockIdx.x * warps + (threadIdx.x >> 5);
     if (g >= C) return;                                   // whole warp leaves together
@@ -137,19 +164,17 @@ fused_tq_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         bt[nt] = *reinterpret_cast<const uint4*>(t + (size_t)g * 1024 + j * 32 + tig * 8);
     }
 
-    const size_t row_stride = (size_t)C * 32;
-    const __nv_bfloat16* xcol = x + (size_t)g * 32 + tig * 8;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
     long long r0 = r_begin;
     long long ra = r0 + gid, rb = ra + 8;
-    uint4 xa = ra < r_end ? ldg_nc_v4(xcol + ra * row_stride) : zero4;
-    uint4 xb = rb < r_end ? ldg_nc_v4(xcol + rb * row_stride) : zero4;
+    uint4 xa = ra < r_end ? load_octet<SILU>(x, ra, C, g, tig) : zero4;
+    uint4 xb = rb < r_end ? load_octet<SILU>(x, rb, C, g, tig) : zero4;
     for (; r0 < r_end; r0 += 16) {
         // prefetch the next slab while this one is in the tensor core
         const long long na = r0 + 16 + gid, nb = na + 8;
-        uint4 nxa = na < r_end ? ldg_nc_v4(xcol + na * row_stride) : zero4;
-        uint4 nxb = nb < r_end ? ldg_nc_v4(xcol + nb * row_stride) : zero4;
+        uint4 nxa = na < r_end ? load_octet<SILU>(x, na, C, g, tig) : zero4;
+        uint4 nxb = nb < r_end ? load_octet<SILU>(x, nb, C, g, tig) : zero4;
 
         float acc[4][4];
 #pragma unroll
@@ -180,6 +205,22 @@ fused_tq_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     }
 }
 
+// FAST launch: warps per CTA and rows per CTA chosen so that small M still spreads over the SMs.
+template <bool SILU>
+static int launch_fast(const void* x, const void* t, int64_t rows, int64_t C, uint8_t* q, void* s, cudaStream_t st)
+{
+    int warps, rows_per_cta;
+    if (rows <= 32) { warps = 2; rows_per_cta = 32; }
+    else if (rows <= 512) { warps = 4; rows_per_cta = 64; }
+    else { warps = 8; rows_per_cta = 128; }
+    const int64_t gy = (rows + rows_per_cta - 1) / rows_per_cta;
+    WUSH_REQUIRE(gy <= 65535, "fused_tq: too many rows");
+    dim3 grid((unsigned)((C + warps - 1) / warps), (unsigned)gy);
+    fused_tq_fast_kernel<SILU><<<grid, warps * 32, 0, st>>>(x, (const __nv_bfloat16*)t, (uint32_t*)q, (__nv_bfloat16*)s,
+                                                            (long long)rows, (int)C, rows_per_cta);
+    return check_launch("fused_tq_fast");
+}
+
 }  // namespace wush
 
 WUSH_API int wush_fused_transform_quant_int4(const void* x, const void* t, int64_t rows, int64_t K,
@@ -202,16 +243,21 @@ WUSH_API int wush_fused_transform_quant_int4(const void* x, const void* t, int64
                                                          (uint4*)q, (__nv_bfloat16*)s, (long long)rows, (int)C);
         return check_launch("fused_tq_exact");
     }
-    // FAST: warps per CTA and rows per CTA chosen so that small M still spreads over the SMs.
-    int warps, rows_per_cta;
-    if (rows <= 32) { warps = 2; rows_per_cta = 32; }
-    else if (rows <= 512) { warps = 4; rows_per_cta = 64; }
-    else { warps = 8; rows_per_cta = 128; }
-    const int64_t gy = (rows + rows_per_cta - 1) / rows_per_cta;
-    WUSH_REQUIRE(gy <= 65535, "fused_tq: too many rows");
-    dim3 grid((unsigned)((C + warps - 1) / warps), (unsigned)gy);
-    fused_tq_fast_kernel<<<grid, warps * 32, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)t,
-                                                      (uint32_t*)q, (__nv_bfloat16*)s, (long long)rows,
-                                                      (int)C, rows_per_cta);
-    return check_launch("fused_tq_fast");
+    return launch_fast<false>(x, t, rows, C, q, s, st);
+}
+
+// No counterpart in the reference: its FFN callers run SiLU, the product with `up` and the cast
+// to bf16 as separate torch kernels between the two projections (an HBM round trip of h).
+WUSH_API int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t, int64_t rows, int64_t K,
+                                                      uint8_t* q, void* s, void* stream)
+{
+    using namespace wush;
+    if (int e = ensure_init()) return e;
+    WUSH_REQUIRE(rows >= 0 && K > 0 && K % 32 == 0, "fused_silu_mul_tq: K must be a positive multiple of 32");
+    if (rows == 0) return WUSH_OK;
+    WUSH_REQUIRE(gate_up && t && q && s, "fused_silu_mul_tq: null pointer");
+    WUSH_REQUIRE(aligned16(gate_up) && aligned16(t) && aligned16(q), "fused_silu_mul_tq: gate_up, t and q must be 16-byte aligned");
+    const int64_t C = K / 32;
+    WUSH_REQUIRE(C <= 65535 * 8, "fused_silu_mul_tq: K too large");
+    return launch_fast<true>(gate_up, t, rows, C, q, s, (cudaStream_t)stream);
 }

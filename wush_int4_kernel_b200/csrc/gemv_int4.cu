@@ -18,42 +18,59 @@
 //     the exact group sum comes out multiplied by 256, which the pre-scaled sx undoes;
 //   * fp32 accumulation over groups per lane, xor-shuffle tree over lanes, fp16 store.
 //
-// The grid is persistent and sized by the occupancy calculator (every CTA resident), rows are
-// dealt round-robin to the warps: with ~40 warps per SM the last round is ~97 % full.
+// Short rows (K <= 4096) are taken two or four at a time so that a lane still has eight loads
+// in flight.  The grid is persistent (every CTA resident) and the units are dealt round-robin to
+// the warps; when the whole job is only a few rounds long, the number of warps per CTA and of
+// CTAs per multiprocessor is chosen so that the rounds come out full.
+// The kernel is launched as a programmatic dependent of the kernel before it (normally the
+// fused transform+quantisation): it gets resident and prefetches while that kernel drains, and
+// reads the activations only after griddepcontrol.wait.
 // Algorithmic HBM bytes per call: 9*N*K/16 (codes + scales of W) + 9*M*K/16 + 2*M*N.
 #include "common.cuh"
 
 namespace wush {
 
-constexpr int GV_THREADS = 256;
-constexpr int GV_WARPS = GV_THREADS / 32;
+constexpr int GV_MAX_WARPS = 8;
 
-// One weight row per warp and trip: lane l owns groups l, l+32, ... (8 per lane and trip, i.e.
-// 144 B of loads in flight per lane).  FIRST is issued before the activation prologue so the
-// weight stream starts while the CTA is still expanding x.
+// The loads of one trip of one warp: 8 slots of 16 bytes of codes + one scale per lane (144 B
+// in flight per lane).  A trip covers R weight rows; row r of the unit owns slots
+// r*U .. r*U+U-1 (U = 8/R), slot u holding group u*32 + lane of that row.
 struct RowLoads {
     uint4 w[8];
     unsigned short s[8];
 };
 
-__device__ __forceinline__ void issue_row_loads(RowLoads& r, const uint8_t* __restrict__ wrow,
-                                                const unsigned short* __restrict__ srow, int gb, int lane, int G)
+template <int R>
+__device__ __forceinline__ void issue_unit_loads(RowLoads& r, const uint8_t* __restrict__ wq,
+                                                 const unsigned short* __restrict__ ws16, int unit, int gb, int lane,
+                                                 int G, int N, size_t K2)
 {
+    constexpr int U = 8 / R;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-        const int g = gb + u * 32 + lane;
-        if (g < G) {
-            r.w[u] = ldg_nc_v4(wrow + (size_t)g * 16);
-            r.s[u] = __ldg(srow + g);
-        } else {
-            r.w[u] = make_uint4(0, 0, 0, 0);
-            r.s[u] = 0;
+    for (int rr = 0; rr < R; ++rr) {
+        const int row = unit * R + rr;
+        const bool live = row < N;
+        const int g0 = gb + lane;
+        // one base address per row; the U slots sit at fixed offsets from it
+        const uint8_t* wp = wq + (size_t)(live ? row : 0) * K2 + (size_t)g0 * 16;
+        const unsigned short* sp = ws16 + (size_t)(live ? row : 0) * G + g0;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (live && g0 + u * 32 < G) {
+                r.w[rr * U + u] = ldg_nc_v4(wp + u * 512);
+                r.s[rr * U + u] = __ldg(sp + u * 32);
+            } else {
+                r.w[rr * U + u] = make_uint4(0, 0, 0, 0);
+                r.s[rr * U + u] = 0;
+            }
         }
     }
 }
 
-template <int MB>
-__global__ void __launch_bounds__(GV_THREADS)
+// R = weight rows per warp and trip.  R > 1 is used when a row has at most 32 * (8/R) groups,
+// so that short rows still put 8 loads per lane in flight; a trip is then a whole unit.
+template <int MB, int R>
+__global__ void __launch_bounds__(GV_MAX_WARPS * 32)
 gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
                  const __nv_bfloat16* __restrict__ xs,     // (MB, G)
                  const uint8_t* __restrict__ wq,           // (N, K/2)
@@ -61,23 +78,36 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
                  __half* __restrict__ y,                   // (MB, N)
                  int N, int K)
 {
+    constexpr int U = 8 / R;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int G = K >> 5;
     uint4* xe = reinterpret_cast<uint4*>(smem_raw);                    // [MB][G] even codes * 16
     uint4* xo = xe + (size_t)MB * G;                                   // [MB][G] odd codes * 16
     float* sxf = reinterpret_cast<float*>(xo + (size_t)MB * G);        // [MB][G] sx / 256
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const size_t K2 = (size_t)K >> 1;
-    const int stride = gridDim.x * GV_WARPS;
-    int n = blockIdx.x * GV_WARPS + warp;
+    const int units = (N + R - 1) / R;
+    const int stride = gridDim.x * warps;
+    int unit = blockIdx.x * warps + warp;
     const unsigned short* ws16 = reinterpret_cast<const unsigned short*>(ws);
 
-    // start the weight stream first: it does not depend on x
-    RowLoads cur;
-    if (n < N) issue_row_loads(cur, wq + (size_t)n * K2, ws16 + (size_t)n * G, 0, lane, G);
+    // While the producer of the activations may still be running, pull this warp's first unit
+    // towards L2 (a prefetch cannot observe stale data), then wait for the producer.
+    if (unit < units) {
+        const int row0 = unit * R, nrows = min(R, N - row0);
+        const uint8_t* cb = wq + (size_t)row0 * K2;
+        for (size_t off = (size_t)lane * 128; off < (size_t)nrows * K2; off += 32 * 128) prefetch_l2(cb + off);
+        const uint8_t* sb = reinterpret_cast<const uint8_t*>(ws16 + (size_t)row0 * G);
+        for (size_t off = (size_t)lane * 128; off < (size_t)nrows * G * 2; off += 32 * 128) prefetch_l2(sb + off);
+    }
+    pdl_wait();
 
-    for (int idx = threadIdx.x; idx < MB * G; idx += GV_THREADS) {
+    // start the weight stream first: it does not depend on the shared-memory prologue
+    RowLoads cur;
+    if (unit < units) issue_unit_loads<R>(cur, wq, ws16, unit, 0, lane, G, N, K2);
+
+    for (int idx = threadIdx.x; idx < MB * G; idx += blockDim.x) {
         uint4 w = *reinterpret_cast<const uint4*>(xq + (size_t)idx * 4);
         uint4 e, o;
         unpack_x16(w.x, e.x, o.x); unpack_x16(w.y, e.y, o.y);
@@ -87,21 +117,21 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
     }
     __syncthreads();
 
-    for (; n < N; n += stride) {
-        const uint8_t* wrow = wq + (size_t)n * K2;
-        const unsigned short* srow = ws16 + (size_t)n * G;
-        float acc[MB];
+    for (; unit < units; unit += stride) {
+        float acc[R][MB];
 #pragma unroll
-        for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-        for (int gb = 0; gb < G; gb += 256) {
-            if (gb) issue_row_loads(cur, wrow, srow, gb, lane, G);
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int g = min(gb + u * 32 + lane, G - 1);          // lanes past the end carry zero weights
+            for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+        for (int gb = 0; gb < G; gb += 32 * U) {
+            if (gb) issue_unit_loads<R>(cur, wq, ws16, unit, gb, lane, G, N, K2);
+#pragma unroll
+            for (int slot = 0; slot < 8; ++slot) {
+                const int g = min(gb + (slot % U) * 32 + lane, G - 1);  // lanes past the end carry zero weights
                 uint4 ae, ao;
-                unpack_x16(cur.w[u].x, ae.x, ao.x); unpack_x16(cur.w[u].y, ae.y, ao.y);
-                unpack_x16(cur.w[u].z, ae.z, ao.z); unpack_x16(cur.w[u].w, ae.w, ao.w);
-                const float sw = bf16_bits_to_f32(cur.s[u]);
+                unpack_x16(cur.w[slot].x, ae.x, ao.x); unpack_x16(cur.w[slot].y, ae.y, ao.y);
+                unpack_x16(cur.w[slot].z, ae.z, ao.z); unpack_x16(cur.w[slot].w, ae.w, ao.w);
+                const float sw = bf16_bits_to_f32(cur.s[slot]);
 #pragma unroll
                 for (int m = 0; m < MB; ++m) {
                     const uint4 ve = xe[m * G + g], vo = xo[m * G + g];
@@ -109,61 +139,129 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
                     d = dp4a_s8(ae.y, ve.y, d); d = dp4a_s8(ao.y, vo.y, d);
                     d = dp4a_s8(ae.z, ve.z, d); d = dp4a_s8(ao.z, vo.z, d);
                     d = dp4a_s8(ae.w, ve.w, d); d = dp4a_s8(ao.w, vo.w, d);
-                    acc[m] = fmaf((float)d, sxf[m * G + g] * sw, acc[m]);
+                    acc[slot / U][m] = fmaf((float)d, sxf[m * G + g] * sw, acc[slot / U][m]);
                 }
             }
         }
-        // next row's first trip goes out before the reduction of this one
-        const int nn = n + stride;
-        if (nn < N) issue_row_loads(cur, wq + (size_t)nn * K2, ws16 + (size_t)nn * G, 0, lane, G);
+        // next unit's first trip goes out before the reduction of this one
+        const int next = unit + stride;
+        if (next < units) issue_unit_loads<R>(cur, wq, ws16, next, 0, lane, G, N, K2);
 #pragma unroll
-        for (int m = 0; m < MB; ++m) {
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int off = 16; off; off >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], off);
-        }
+            for (int m = 0; m < MB; ++m) {
+#pragma unroll
+                for (int off = 16; off; off >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], off);
+            }
         if (lane == 0) {
 #pragma unroll
-            for (int m = 0; m < MB; ++m) y[(size_t)m * N + n] = __float2half_rn(acc[m]);
+            for (int r = 0; r < R; ++r) {
+                const int n = unit * R + r;
+                if (n < N) {
+#pragma unroll
+                    for (int m = 0; m < MB; ++m) y[(size_t)m * N + n] = __float2half_rn(acc[r][m]);
+                }
+            }
         }
     }
 }
 
 size_t gemv_smem_bytes(int M, int64_t K) { return (size_t)M * (K / 32) * (16 + 16 + 4); }
 
-template <int MB>
+// Shape of the persistent grid: `warps` per CTA and `ctas` per multiprocessor such that the
+// units, dealt round-robin to all resident warps, fill whole rounds (a half-empty last round
+// costs a full memory latency at a fraction of the bandwidth).
+struct GemvShape { int warps, ctas_per_sm; };
+
+template <int MB, int R>
+static GemvShape pick_shape(size_t smem, long long units)
+{
+    struct Cache { size_t smem; int per_sm[GV_MAX_WARPS + 1]; };
+    static thread_local Cache cache = {~size_t(0), {}};
+    if (cache.smem != smem) {
+        for (int w = 4; w <= GV_MAX_WARPS; ++w) {
+            int q = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_dp4a_kernel<MB, R>, w * 32, smem) != cudaSuccess) q = 0;
+            cache.per_sm[w] = q;
+        }
+        cache.smem = smem;
+    }
+    const int sms = sm_count();
+    // Many rounds: warps drift apart and the last round costs little; take the most resident
+    // warps in the fewest CTAs.  Few rounds: search for a shape that fills them.
+    if (cache.per_sm[GV_MAX_WARPS] >= 1 &&
+        (double)units / ((double)sms * GV_MAX_WARPS * cache.per_sm[GV_MAX_WARPS]) >= 8.0)
+        return {GV_MAX_WARPS, cache.per_sm[GV_MAX_WARPS]};
+    GemvShape best = {8, 1};
+    double best_score = -1.0;
+    for (int w = 4; w <= GV_MAX_WARPS; ++w) {
+        for (int c = 1; c <= cache.per_sm[w]; ++c) {
+            const int resident = w * c;
+            if (resident < 16 && (w < GV_MAX_WARPS || c < cache.per_sm[w])) continue;      // too few loads in flight
+            if (resident > 64) continue;
+            const double rounds = (double)units / ((double)sms * resident);
+            const double whole = rounds <= 1.0 ? 1.0 : (double)(long long)(rounds + 0.999999);
+            // fullness of the rounds; a mild preference for more resident warps and for fewer,
+            // larger CTAs (each CTA expands the activations for itself)
+            const double score = rounds / whole + 0.002 * resident + 0.0002 * w;
+            if (score > best_score) { best_score = score; best = {w, c}; }
+        }
+    }
+    return best;
+}
+
+template <int MB, int R>
 static int launch_gemv(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t N,
                        int64_t K, void* y, cudaStream_t st)
 {
     const size_t smem = gemv_smem_bytes(MB, K);
-    // resident CTAs per SM for this shared-memory size (a host-side query, cached per size)
-    static thread_local size_t cached_smem = ~size_t(0);
-    static thread_local int cached_per_sm = 1;
-    if (cached_smem != smem) {
-        int q = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_dp4a_kernel<MB>, GV_THREADS, smem) != cudaSuccess || q < 1) q = 1;
-        cached_smem = smem;
-        cached_per_sm = q;
+    const long long units = (N + R - 1) / R;
+    // the choice depends on the shape only: remember the last one (decode calls repeat shapes)
+    static thread_local long long last_units = -1;
+    static thread_local size_t last_smem = 0;
+    static thread_local GemvShape shape = {8, 1};
+    if (last_units != units || last_smem != smem) {
+        shape = pick_shape<MB, R>(smem, units);
+        last_units = units;
+        last_smem = smem;
     }
-    const int per_sm = cached_per_sm;
-    // persistent grid: every CTA resident at once, rows dealt round-robin to the warps
-    long long ctas = (long long)sm_count() * per_sm;
-    const long long needed = (N + GV_WARPS - 1) / GV_WARPS;
+    long long ctas = (long long)sm_count() * shape.ctas_per_sm;
+    const long long needed = (units + shape.warps - 1) / shape.warps;
     if (ctas > needed) ctas = needed;
-    gemv_dp4a_kernel<MB><<<(unsigned)ctas, GV_THREADS, smem, st>>>((const uint32_t*)xq, (const __nv_bfloat16*)xs, wq,
-                                                                   (const __nv_bfloat16*)ws, (__half*)y, (int)N, (int)K);
+    cudaError_t e = launch_dependent(gemv_dp4a_kernel<MB, R>, dim3((unsigned)ctas), dim3(shape.warps * 32), smem, st,
+                                     (const uint32_t*)xq, (const __nv_bfloat16*)xs, wq, (const __nv_bfloat16*)ws, (__half*)y,
+                                     (int)N, (int)K);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "gemv launch: %s", cudaGetErrorString(e));
     return check_launch("gemv_dp4a");
+}
+
+template <int MB, int R>
+static cudaError_t set_attr()
+{
+    return cudaFuncSetAttribute(gemv_dp4a_kernel<MB, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 }
 
 int gemv_set_attributes()
 {
-    const int max_smem = 200 * 1024;
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(gemv_dp4a_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(gemv_dp4a_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(gemv_dp4a_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)) != cudaSuccess)
+    if ((e = set_attr<1, 1>()) != cudaSuccess || (e = set_attr<1, 2>()) != cudaSuccess || (e = set_attr<1, 4>()) != cudaSuccess ||
+        (e = set_attr<2, 1>()) != cudaSuccess || (e = set_attr<2, 2>()) != cudaSuccess || (e = set_attr<2, 4>()) != cudaSuccess ||
+        (e = set_attr<3, 1>()) != cudaSuccess || (e = set_attr<3, 2>()) != cudaSuccess ||
+        (e = set_attr<4, 1>()) != cudaSuccess || (e = set_attr<4, 2>()) != cudaSuccess)
         return fail(WUSH_ERR_CUDA, "gemv: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
+}
+
+template <int MB>
+static int launch_rows(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t N, int64_t K,
+                       void* y, cudaStream_t st)
+{
+    const int64_t slots = (K / 32 + 31) / 32;              // 16-byte loads per lane and row
+    if constexpr (MB <= 2) {
+        if (slots <= 2) return launch_gemv<MB, 4>(xq, xs, wq, ws, N, K, y, st);
+    }
+    if (slots <= 4) return launch_gemv<MB, 2>(xq, xs, wq, ws, N, K, y, st);
+    return launch_gemv<MB, 1>(xq, xs, wq, ws, N, K, y, st);
 }
 
 // M in 1..4, shared memory must fit (checked by the dispatcher).
@@ -171,10 +269,10 @@ int gemv_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const vo
                   int64_t K, void* y, cudaStream_t st)
 {
     switch (M) {
-        case 1: return launch_gemv<1>(xq, xs, wq, ws, N, K, y, st);
-        case 2: return launch_gemv<2>(xq, xs, wq, ws, N, K, y, st);
-        case 3: return launch_gemv<3>(xq, xs, wq, ws, N, K, y, st);
-        case 4: return launch_gemv<4>(xq, xs, wq, ws, N, K, y, st);
+        case 1: return launch_rows<1>(xq, xs, wq, ws, N, K, y, st);
+        case 2: return launch_rows<2>(xq, xs, wq, ws, N, K, y, st);
+        case 3: return launch_rows<3>(xq, xs, wq, ws, N, K, y, st);
+        case 4: return launch_rows<4>(xq, xs, wq, ws, N, K, y, st);
     }
     return fail(WUSH_ERR_INVALID_ARGUMENT, "gemv: M=%lld outside 1..4", (long long)M);
 }

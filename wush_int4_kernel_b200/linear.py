@@ -127,7 +127,10 @@ class RowParallelW4A4Linear:
                                 ws[:, self.k0 // 32:self.k1 // 32].contiguous())
 
     def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
-        y = self.local(x_local)
+        return self.reduce(self.local(x_local))
+
+    def reduce(self, y: torch.Tensor) -> torch.Tensor:
+        """All-reduce (sum in fp32) of this rank's partial product."""
         if not self.reduce_output or self.world == 1:
             return y
         import torch.distributed as dist
@@ -156,7 +159,25 @@ class TensorParallelFFN:
                                      wq_d[:, self.i0 // 2:self.i1 // 2].contiguous(),
                                      ws_d[:, self.i0 // 32:self.i1 // 32].contiguous())
 
+    @classmethod
+    def from_local_shards(cls, gate_up: tuple, down: tuple, world: int, rank: int, group=None) -> "TensorParallelFFN":
+        """Builds the block from tensors that are ALREADY this rank's shards (gate rows then up
+        rows of the local intermediate slice; down-projection columns of the same slice), so a
+        rank never has to hold the unsharded layer."""
+        self = cls(gate_up, down, world=1, rank=0, group=group)
+        self.down.world, self.down.rank = world, rank
+        return self
+
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        gu = self.gate_up(x)
+        # SiLU(gate) * up -> bf16 -> transform -> quantise in one kernel: h never goes to HBM
+        lead = gu.shape[:-1]
+        hq, hs = _ops().fused_silu_mul_transform_quant_int4(gu.reshape(-1, gu.shape[-1]), self.down.local.t)
+        y = w4a4_product(hq, hs, self.down.local.wq, self.down.local.ws).reshape(*lead, self.down.local.out_features)
+        return self.down.reduce(y)
+
+    def reference_call(self, x: torch.Tensor) -> torch.Tensor:
+        """The same block as a composition of the single ops (separate activation kernels)."""
         gu = self.gate_up(x)
         half = gu.shape[-1] // 2
         h = (torch.nn.functional.silu(gu[..., :half].float()) * gu[..., half:].float()).to(torch.bfloat16)
