@@ -84,6 +84,21 @@ def gemm_ts(xq, wq, alpha: float, alpha_dev=None):
     return y
 
 
+def gemm_ts_ws(xq, wq, alpha: float, alpha_dev=None):
+    """Per-tensor product with caller scratch; returns (y, scratch bytes used, error word)."""
+    lib = capi.load()
+    K = wq.shape[1] * 2
+    M, N = xq.numel() // (K // 2), wq.shape[0]
+    y = torch.empty(M, N, dtype=torch.float16, device=xq.device)
+    nbytes = lib.wush_w4a4_gemm_tensor_scale_workspace_bytes(M, N, K)
+    work = torch.full((max(nbytes, 4),), 0x55, dtype=torch.uint8, device=xq.device)
+    capi.check(lib.wush_w4a4_gemm_tensor_scale_ws(xq.data_ptr(), wq.data_ptr(), M, N, K, alpha,
+                                                  alpha_dev.data_ptr() if alpha_dev is not None else None, y.data_ptr(),
+                                                  work.data_ptr() if nbytes else None, nbytes, _stream()), "gemm_ts_ws")
+    flag = int(work[:4].view(torch.int32).item()) if nbytes else 0
+    return y, nbytes, flag
+
+
 def tile_selftest(a, b, layout_mode: int = 0):
     lib = capi.load()
     n = b.shape[0]

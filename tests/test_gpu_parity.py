@@ -349,6 +349,29 @@ def test_per_tensor_route(dev, orc, golden):
         assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 264, 384), (512, 1000, 1024), (4096, 4096, 4096)])
+def test_per_tensor_tile_route(dev, orc, M, N, K):
+    """tcgen05 kind::i8 tiles for the per-tensor product: same bits as the scratch-free kernel
+    (and as the oracle where the oracle finishes quickly), error word clean."""
+    from tests import cabi
+    gen = torch.Generator(device=dev).manual_seed(M + N + K)
+    xq = torch.randint(0, 256, (M, K // 2), generator=gen, device=dev, dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=gen, device=dev, dtype=torch.uint8)
+    alpha = 3.1e-4
+    y, nbytes, flag = cabi.gemm_ts_ws(xq, wq, alpha)
+    assert nbytes > 0 and flag == 0
+    assert torch.equal(y, cabi.gemm_ts(xq, wq, alpha))
+    a = torch.tensor([alpha], dtype=torch.float32, device=dev)
+    y2, _, flag2 = cabi.gemm_ts_ws(xq, wq, 0.0, a)
+    assert flag2 == 0 and torch.equal(y, y2)
+    if M * N * K <= 1 << 28:
+        yo, _ = orc.gemm_tensor_scale(xq.cpu().numpy(), wq.cpu().numpy(), alpha)
+        assert np.array_equal(orc.bits(y), yo)
+    # the binding allocates the scratch itself
+    from my_int4 import _C
+    assert torch.equal(_C.w4a4_gemm_cutlass(xq, wq, alpha), y)
+
+
 # ------------------------------------------------------------------------------------------
 # CUDA Graph safety (reference tests/test_p13.py:45-66, tests/test_p12.py:142-152)
 # ------------------------------------------------------------------------------------------

@@ -36,6 +36,8 @@ SIGNATURES = {
     "wush_group_partials": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "wush_quant_int4_tensor_scale": (_int, [_vp, _i64, _f32, _vp, _vp, _vp]),
     "wush_w4a4_gemm_tensor_scale": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "wush_w4a4_gemm_tensor_scale_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "wush_w4a4_gemm_tensor_scale_ws": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _sz, _vp]),
 }
 
 _lib = None

@@ -252,8 +252,11 @@ torch::Tensor gemm_ts(torch::Tensor xq, torch::Tensor wq, float alpha, const flo
     TORCH_CHECK(M * K2 == xq.numel(), "xq numel must equal M*K/2 (K from wq)");
     const at::cuda::OptionalCUDAGuard guard(xq.device());
     auto y = torch::empty({M, N}, xq.options().dtype(torch::kHalf));
-    check_status(wush_w4a4_gemm_tensor_scale(xq.data_ptr<uint8_t>(), wq.data_ptr<uint8_t>(), M, N, K2 * 2, alpha,
-                                             alpha_dev, y.data_ptr(), stream_of(xq)),
+    const size_t nbytes = wush_w4a4_gemm_tensor_scale_workspace_bytes(M, N, K2 * 2);
+    torch::Tensor work;
+    if (nbytes) work = torch::empty({(int64_t)nbytes}, xq.options());
+    check_status(wush_w4a4_gemm_tensor_scale_ws(xq.data_ptr<uint8_t>(), wq.data_ptr<uint8_t>(), M, N, K2 * 2, alpha, alpha_dev,
+                                                y.data_ptr(), nbytes ? work.data_ptr() : nullptr, nbytes, stream_of(xq)),
                  op);
     return y;
 }

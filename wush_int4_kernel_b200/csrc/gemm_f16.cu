@@ -24,6 +24,7 @@
 //                        rotation -> epilogue warps tcgen05.ld, scale by 2^(e_m+e_n), fp16 store
 // Algorithmic traffic: the pre-pass reads 9/16 B and writes 2 B per operand element; the GEMM
 // reads fp16 operands (L2-resident across the M tiles that share a weight tile).
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -80,7 +81,7 @@ dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restric
 // ------------------------------------------------------------------------------------------------
 // GEMM
 // ------------------------------------------------------------------------------------------------
-constexpr int FM = 128, FN = 256, FK = 64;                     // tile; K elements per stage (128 B rows)
+constexpr int FM = 128, FN = 256;                               // tile; a stage holds 128 bytes of K per row
 constexpr int F_STAGES = 4, F_ACC = 2;
 constexpr int F_THREADS = 256;                                  // warp 0 TMA, warp 1 MMA, warps 4-7 epilogue
 constexpr int FA_BYTES = FM * 128, FB_BYTES = FN * 128;
@@ -107,11 +108,25 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
 }
 
+// Epilogue constants of the two operand kinds the tile kernel serves.
+//   fp16-folded operands: y = acc * 2^(e_m + e_n), one factor per row of each operand;
+//   int8 codes (per-tensor scale): y = alpha * acc, alpha a host value or a device scalar.
+struct TileScale {
+    const float* fa;
+    const float* fb;
+    float alpha;
+    const float* alpha_dev;
+};
+
+// I8 = false: fp16 operands, 64 elements per 128-byte stage row, tcgen05.mma kind::f16 (K = 16);
+// I8 = true:  int8 operands, 128 elements per stage row, kind::i8 (K = 32), int32 accumulators.
+// Either way a stage row is 128 bytes and one MMA advances 32 bytes along it.
+template <bool I8>
 __global__ void __launch_bounds__(F_THREADS, 1)
-gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const float* __restrict__ fa, const float* __restrict__ fb, __half* __restrict__ y, int M, int N, int K,
-                int* __restrict__ err)
+gemm_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const TileScale sc, __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
 {
+    constexpr int FK = I8 ? 128 : 64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + F_BARS);
@@ -168,7 +183,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else if (warp == 1) {
         if (lane == 0) {
             uint32_t slot = 0, phase = 0, ab = 0, aphase = 0;
-            const uint32_t idesc = tc::idesc_f16(FN);
+            const uint32_t idesc = I8 ? tc::idesc_i8(FN) : tc::idesc_f16(FN);
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 if (!tc::mbar_wait(&acc_empty[ab], aphase ^ 1)) { ok = false; break; }
@@ -178,9 +193,14 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tc::tc_fence_after();
                     const uint32_t sa = tc::smem_u32(smem + slot * F_STAGE), sb = sa + FA_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < FK / 16; ++kk)                       // 32 bytes further along K inside the swizzled row
-                        mma_f16(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
-                                (ks | kk) ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk) {                           // 32 bytes further along K inside the swizzled row
+                        if constexpr (I8)
+                            tc::mma_i8(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
+                                       (ks | kk) ? 1u : 0u);
+                        else
+                            mma_f16(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
+                                    (ks | kk) ? 1u : 0u);
+                    }
                     tc::mma_commit(&empty[slot]);                              // stage free once these MMAs retire
                     if (++slot == F_STAGES) { slot = 0; phase ^= 1; }
                 }
@@ -203,7 +223,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
-            const float fm = (m < M) ? fa[m] : 0.f;
+            float fm;
+            if constexpr (I8) fm = sc.alpha_dev ? __ldg(sc.alpha_dev) : sc.alpha;
+            else fm = (m < M) ? sc.fa[m] : 0.f;
 #pragma unroll 1
             for (int c = 0; c < FN / 32; ++c) {
                 uint32_t v[32];
@@ -220,15 +242,24 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int v8 = 0; v8 < 4; ++v8) {
                         if (n + v8 * 8 + 8 <= N) {
-                            const float4 f0 = *reinterpret_cast<const float4*>(fb + n + v8 * 8);
-                            const float4 f1 = *reinterpret_cast<const float4*>(fb + n + v8 * 8 + 4);
-                            const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
                             uint32_t o[4];
+                            if constexpr (I8) {
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) {
-                                __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
-                                                              __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
-                                o[p] = *reinterpret_cast<uint32_t*>(&h);
+                                for (int p = 0; p < 4; ++p) {                  // |acc| < 2^24: the conversion is exact
+                                    __half2 h = __floats2half2_rn(__fmul_rn(fm, (float)(int)v[v8 * 8 + 2 * p]),
+                                                                  __fmul_rn(fm, (float)(int)v[v8 * 8 + 2 * p + 1]));
+                                    o[p] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                            } else {
+                                const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
+                                const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
+                                const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+                                for (int p = 0; p < 4; ++p) {
+                                    __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
+                                                                  __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
+                                    o[p] = *reinterpret_cast<uint32_t*>(&h);
+                                }
                             }
                             *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
                         }
@@ -252,8 +283,9 @@ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 int f16_set_attributes()
 {
     if (int s = resolve_tensor_map_encoder()) return s;
-    cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
-    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "f16 GEMM: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    cudaError_t e = cudaFuncSetAttribute(gemm_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "tile GEMM: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
 
@@ -287,12 +319,81 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     if (int s = check_launch("dequant_f16")) return s;
     CUtensorMap ma, mb;
     int s;
-    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, FK, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
-    if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b16, K, N, FK, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b16, K, N, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     const int64_t tiles = ((M + FM - 1) / FM) * ((N + FN - 1) / FN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    gemm_f16_kernel<<<grid, F_THREADS, F_TOTAL, st>>>(ma, mb, fa, fb, (__half*)y, (int)M, (int)N, (int)K, err);
+    const TileScale sc = {fa, fb, 0.f, nullptr};
+    gemm_tile_kernel<false><<<grid, F_THREADS, F_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
     return check_launch("gemm_f16");
+}
+
+// ------------------------------------------------------------------------------------------------
+// Per-tensor-scale product on the same tile kernel (kind::i8): y = alpha * (qa . qw)
+// ------------------------------------------------------------------------------------------------
+// A pre-pass widens the packed nibbles of both operands to int8 rows in the scratch; the tile
+// kernel then runs tcgen05.mma kind::i8 with N = 256 over the whole K into int32 accumulators and
+// scales once in the epilogue -- the shape in which the int8 tensor path runs near its peak.
+namespace {
+__global__ void __launch_bounds__(256)
+widen_s8_kernel(const uint4* __restrict__ q, uint4* __restrict__ out, long long n_vec)     // 32 codes per step
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+        const uint4 w = ldg_nc_v4(q + i);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // byte b of the word holds codes 2b (low nibble) and 2b + 1 (high nibble)
+            const uint32_t lo = ww[j] & 0x0F0F0F0Fu, hi = (ww[j] >> 4) & 0x0F0F0F0Fu;
+            const uint32_t slo = lo | ((lo & 0x08080808u) * 0x1Eu);                // sign bit of each nibble copied into bits 4..7
+            const uint32_t shi = hi | ((hi & 0x08080808u) * 0x1Eu);
+            o[2 * j] = __byte_perm(slo, shi, 0x5140);                              // codes 0..3: lo0 hi0 lo1 hi1
+            o[2 * j + 1] = __byte_perm(slo, shi, 0x7362);                          // codes 4..7: lo2 hi2 lo3 hi3
+        }
+        out[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+        out[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+}  // namespace
+
+bool i8_tile_supported(int64_t M, int64_t N, int64_t K) { return M >= 1 && K % 128 == 0 && N % 8 == 0; }
+
+// scratch: error word | int8 activations (M x K) | int8 weights (N x K)
+size_t i8_tile_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    return 256 + align256((size_t)M * K) + align256((size_t)N * K);
+}
+
+int i8_tile_dispatch(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N, int64_t K, float alpha, const float* alpha_dev,
+                     void* y, void* workspace, size_t workspace_bytes, cudaStream_t st)
+{
+    if (!aligned16(y) || !aligned16(workspace))
+        return fail(WUSH_ERR_INVALID_ARGUMENT, "gemm_tensor_scale: output and workspace must be 16-byte aligned");
+    if (workspace_bytes < i8_tile_workspace_bytes(M, N, K))
+        return fail(WUSH_ERR_WORKSPACE, "gemm_tensor_scale: workspace of %zu bytes needed, %zu given",
+                    i8_tile_workspace_bytes(M, N, K), workspace_bytes);
+    uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+    int* err = reinterpret_cast<int*>(base);
+    uint8_t* a8 = base + 256;
+    uint8_t* b8 = a8 + align256((size_t)M * K);
+    cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    const long long cap = (long long)sm_count() * 16;
+    const long long va = M * K / 32, vb = N * K / 32;
+    widen_s8_kernel<<<(unsigned)std::min<long long>((va + 255) / 256, cap), 256, 0, st>>>((const uint4*)xq, (uint4*)a8, va);
+    widen_s8_kernel<<<(unsigned)std::min<long long>((vb + 255) / 256, cap), 256, 0, st>>>((const uint4*)wq, (uint4*)b8, vb);
+    if (int s = check_launch("widen_s8")) return s;
+    CUtensorMap ma, mb;
+    int s;
+    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a8, K, M, 128, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b8, K, N, 128, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    const int64_t tiles = ((M + FM - 1) / FM) * ((N + FN - 1) / FN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const TileScale sc = {nullptr, nullptr, alpha, alpha_dev};
+    gemm_tile_kernel<true><<<grid, F_THREADS, F_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
+    return check_launch("gemm_i8_tile");
 }
 
 }  // namespace wush

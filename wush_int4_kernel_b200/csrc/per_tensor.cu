@@ -9,6 +9,11 @@
 
 namespace wush {
 
+bool i8_tile_supported(int64_t M, int64_t N, int64_t K);
+size_t i8_tile_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int i8_tile_dispatch(const uint8_t*, const uint8_t*, int64_t, int64_t, int64_t, float, const float*, void*, void*, size_t,
+                     cudaStream_t);
+
 __global__ void __launch_bounds__(256)
 quant_ts_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ q, float inv_host,
                 const float* __restrict__ inv_dev, long long n_chunks)   // chunk = 8 bf16 -> 4 bytes
@@ -30,8 +35,8 @@ quant_ts_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ q, float inv
     }
 }
 
-// One warp per output row n and 8 rows m per CTA would be the tuned shape; this first
-// version keeps one thread per output with 16-byte loads and dp4a (exact int32).
+// Small shapes and callers without scratch: one thread per output with 16-byte loads and dp4a
+// (exact int32).  Large M with scratch goes to the tcgen05 tile kernel (gemm_f16.cu).
 __global__ void __launch_bounds__(256)
 gemm_ts_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ wq, __half* __restrict__ y,
                float alpha_host, const float* __restrict__ alpha_dev, int M, int N, int K)
@@ -94,4 +99,28 @@ WUSH_API int wush_w4a4_gemm_tensor_scale(const uint8_t* xq, const uint8_t* wq, i
     WUSH_REQUIRE(grid.y <= 65535, "gemm_tensor_scale: M too large");
     gemm_ts_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(xq, wq, (__half*)y, alpha, alpha_dev, (int)M, (int)N, (int)K);
     return check_launch("gemm_tensor_scale");
+}
+
+// Rows from which the tensor-core tile route pays for its widening pre-pass.
+static const int64_t TS_TILE_MIN_ROWS = 128;
+
+WUSH_API size_t wush_w4a4_gemm_tensor_scale_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    using namespace wush;
+    if (M < TS_TILE_MIN_ROWS || N <= 0 || K <= 0 || K > (1 << 18) || !i8_tile_supported(M, N, K)) return 0;
+    return i8_tile_workspace_bytes(M, N, K);
+}
+
+WUSH_API int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N, int64_t K, float alpha,
+                                            const float* alpha_dev, void* y, void* workspace, size_t workspace_bytes,
+                                            void* stream)
+{
+    using namespace wush;
+    if (int e = ensure_init()) return e;
+    const size_t need = wush_w4a4_gemm_tensor_scale_workspace_bytes(M, N, K);
+    if (need == 0 || !workspace || workspace_bytes == 0)
+        return wush_w4a4_gemm_tensor_scale(xq, wq, M, N, K, alpha, alpha_dev, y, stream);
+    WUSH_REQUIRE(xq && wq && y, "gemm_tensor_scale: null pointer");
+    WUSH_REQUIRE(aligned16(xq) && aligned16(wq), "gemm_tensor_scale: codes must be 16-byte aligned");
+    return i8_tile_dispatch(xq, wq, M, N, K, alpha, alpha_dev, y, workspace, workspace_bytes, (cudaStream_t)stream);
 }
