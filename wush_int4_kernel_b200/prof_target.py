@@ -3,6 +3,7 @@ operator a few times on synthetic operands so that ``ncu -k regex:<kernel> -c <n
 small, self-contained process to capture.
 
     python -m wush_int4_kernel_b200.prof_target gemm  M N K [reps]
+    python -m wush_int4_kernel_b200.prof_target gemm_ts M N K [reps]     (per-tensor scale)
     python -m wush_int4_kernel_b200.prof_target fused M K   [reps]
     python -m wush_int4_kernel_b200.prof_target quant M K   [reps]
 
@@ -40,6 +41,13 @@ def main(argv):
             fn = lambda: _C.w4a4_gemv_multi(xq, xs, wq, ws)
         else:
             fn = lambda: _C.w4a4_gemm_s4(xq, xs, wq, ws)
+        work = 2.0 * M * N * K
+    elif op == "gemm_ts":
+        M, N, K = map(int, argv[1:4])
+        reps = int(argv[4]) if len(argv) > 4 else 5
+        xq, _ = _codes(M, K, gen, dev)
+        wq, _ = _codes(N, K, gen, dev)
+        fn = lambda: _C.w4a4_gemm_cutlass(xq, wq, 1e-3)
         work = 2.0 * M * N * K
     elif op in ("fused", "quant"):
         M, K = map(int, argv[1:3])
