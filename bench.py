@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -237,13 +238,21 @@ def run_gpu_arm(args):
         a, b = quantise_activations(x_dev, t_bf16)
         y_host.copy_(w4a4_product(a, b, wq, ws), non_blocking=True)
 
+    # The same step as the user-facing replay form: pinned-host -> device copy, the two kernels and
+    # the device -> pinned-host copy captured into one CUDA Graph per (input buffer, weight copy).
+    period = 4 * copies // math.gcd(4, copies)
+    e2e_graphs = [timing.capture(lambda i=i: e2e_step(i))[0] for i in range(period)]
+
+    def e2e_replay(i):
+        e2e_graphs[i % period].replay()
+
     for i in range(max(args.warmup, 3)):
-        e2e_step(i)
+        e2e_replay(i)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        e2e_step(i)
+        e2e_replay(i)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -251,9 +260,16 @@ def run_gpu_arm(args):
         tmax = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         e2e_ms = float(tmax.item())
+    # the host buffer of the last replay must hold the product of its inputs
+    torch.cuda.synchronize()
+    last = args.steps - 1
+    a, b = quantise_activations(x_host[last % 4].to(dev), t_bf16)
+    expect = w4a4_product(a, b, *weights[last % copies]).cpu()
+    e2e_check = bool(torch.equal(expect, y_host))
     e2e_tops = 2.0 * M * N_DIM * K_DIM / (e2e_ms / args.steps * 1e-3) / 1e12
     e2e = {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": 2 * M * K_DIM * world,
-           "d2h_bytes_per_step": 2 * M * N_DIM, "us_per_step": 1e3 * e2e_ms / args.steps}
+           "d2h_bytes_per_step": 2 * M * N_DIM, "us_per_step": 1e3 * e2e_ms / args.steps,
+           "form": "CUDA Graph of pinned H2D copy -> transform+quant -> product -> pinned D2H copy"}
 
     if rank != 0:
         if world > 1:
@@ -286,6 +302,7 @@ def run_gpu_arm(args):
         "layer_hbm_frac": algorithmic_bytes_layer(M, n_local, K_DIM) / (ms_per_step * 1e-3) / 1e9 / peak,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        "e2e_check": e2e_check,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
