@@ -85,6 +85,15 @@ fused_tq_exact_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 // ----------------------------------------------------------------------------------------
 // FAST
 // ----------------------------------------------------------------------------------------
+// D = A * B (no accumulator input: saves clearing the registers)
+__device__ __forceinline__ void mma_bf16_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                     uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -107,14 +116,17 @@ __device__ __forceinline__ void quantise_row_octet(const float (&v)[8], uint32_t
     *sbits = sigma_clip_scale(s1, s2, &scale);
     const float inv = __frcp_rn(scale);
     const float magic = 12582912.f;                       // 1.5 * 2^23: low mantissa bits = rint()
+    // bits(f) = bits(magic) + q exactly, so sum_e bits(f_e) * 16^e (mod 2^32) is the packed word of the
+    // offset nibbles q + 8 plus a constant; one multiply-add per element, then the constant comes
+    // off and the offset is undone by flipping bit 3 of every nibble.
     uint32_t w = 0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         float f = fmaf(v[e], inv, magic);
         f = fminf(fmaxf(f, magic - 7.f), magic + 7.f);
-        w |= (__float_as_uint(f) & 0xFu) << (4 * e);
+        w = __float_as_uint(f) * (1u << (4 * e)) + w;
     }
-    *word = w;
+    *word = (w - (0x4B400000u - 8u) * 0x11111111u) ^ 0x88888888u;
 }
 
 // SiLU(gate) * up of 8 fp16 pairs -> 8 bf16 in one 16-byte register set.  fp32 throughout:
@@ -179,8 +191,7 @@ fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict
         float acc[4][4];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
-            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-            mma_bf16_16816(acc[nt], xa.x, xb.x, xa.y, xb.y, bt[nt].x, bt[nt].y);
+            mma_bf16_16816_first(acc[nt], xa.x, xb.x, xa.y, xb.y, bt[nt].x, bt[nt].y);
             mma_bf16_16816(acc[nt], xa.z, xb.z, xa.w, xb.w, bt[nt].z, bt[nt].w);
         }
         float va[8], vb[8];
