@@ -181,6 +181,27 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
                                    int64_t K, float alpha, const float* alpha_dev, void* y,
                                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* --- multi-GPU: one-shot all-reduce of small fp16 partial products over NVLink peer memory ------
+ * No counterpart in the reference (single GPU).  The row-parallel down projection of a
+ * tensor-parallel FFN block ends in a sum over ranks; at decode sizes a library all-reduce costs
+ * several times the sharded product.  One process per GPU of one node:
+ *   wush_comm_create   allocates this rank's exchange buffer (two slots of slot_bytes, flags, state).
+ *                      The ONLY call of this library that allocates device memory; set-up time.
+ *   wush_comm_export   64-byte CUDA IPC handle of that buffer, to be sent to every other rank;
+ *   wush_comm_connect  maps a peer's buffer from its handle (once per peer);
+ *   wush_comm_allreduce_f16  out[i] = fp16( sum over ranks r = 0..world-1 of fp32(partial_r[i]) ), n % 8 == 0,
+ *                      2n <= slot_bytes; every rank must call it the same number of times with the
+ *                      same n.  One kernel launch, no host synchronisation, capturable; a rank waits for
+ *                      its peers inside the kernel for about a second at most, then records an error;
+ *   wush_comm_error    (synchronous) 1 if a wait ever ran out on this rank;
+ *   wush_comm_destroy  unmaps and frees. */
+int wush_comm_create(int rank, int world, size_t slot_bytes, void** comm);
+int wush_comm_export(void* comm, void* handle64);
+int wush_comm_connect(void* comm, int peer_rank, const void* handle64);
+int wush_comm_allreduce_f16(void* comm, const void* partial, void* out, int64_t n, void* stream);
+int wush_comm_error(void* comm, int* error);
+int wush_comm_destroy(void* comm);
+
 #ifdef __cplusplus
 }
 #endif

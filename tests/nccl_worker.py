@@ -28,6 +28,39 @@ def main():
     y = row(x[:, k0:k1].contiguous())
     rel = ((y.float() - full.float()).norm() / full.float().norm()).item()
     assert rel <= 2e-3, rel
+    # one-shot all-reduce over peer memory: bit-identical to the fp32 sum of the fp16 partials in rank order,
+    # eager and replayed from a CUDA Graph, several steps in a row (the two slots alternate)
+    from wush_int4_kernel_b200.peer_reduce import PeerAllReduce
+    peer = PeerAllReduce(max_elements=64 * 768)
+    gen_r = torch.Generator(device="cuda").manual_seed(100 + rank)
+    for step, rows in enumerate([1, 6, 64, 6, 1]):
+        part = torch.randn(rows, 768, generator=gen_r, device="cuda").to(torch.float16)
+        gathered = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(gathered, part)
+        acc = torch.zeros(rows, 768, device="cuda")
+        for g in gathered:
+            acc = acc + g.float()
+        got = peer(part)
+        assert torch.equal(got, acc.to(torch.float16)), f"peer all-reduce differs at step {step}"
+    part = torch.randn(8, 768, generator=gen_r, device="cuda").to(torch.float16)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        warm = peer(part)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        out = peer(part)
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, warm), "graph replay differs from the eager call"
+    assert peer.error() == 0
+    row2 = RowParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, peer_reduce=peer)
+    y2 = row2(x[:, k0:k1].contiguous())
+    assert ((y2.float() - full.float()).norm() / full.float().norm()).item() <= 2e-3
+    peer.close()
     dist.barrier()
     print(f"rank {rank} ok", flush=True)
     dist.destroy_process_group()

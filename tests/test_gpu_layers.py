@@ -118,3 +118,29 @@ def test_fused_silu_mul_transform_quant(setup, rows, K):
     assert torch.equal(s, s_ref) and torch.equal(q, q_ref)
     with pytest.raises(RuntimeError):
         _C.fused_silu_mul_transform_quant_int4(gate_up.float(), t)
+
+
+def test_peer_allreduce_single_rank():
+    """World of one through the C ABI: the kernel's copy / publish / wait / reduce path with no
+    peers -- the result is the input, step after step, eager and replayed from a graph."""
+    import ctypes
+    from wush_int4_kernel_b200 import capi
+    lib = capi.load()
+    comm = ctypes.c_void_p()
+    capi.check(lib.wush_comm_create(0, 1, 256 * 1024, ctypes.byref(comm)), "comm_create")
+    try:
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        stream = torch.cuda.current_stream().cuda_stream
+        for n in (8, 8192, 131072, 8192):
+            part = torch.randn(n, generator=gen, device="cuda").to(torch.float16)
+            out = torch.zeros_like(part)
+            capi.check(lib.wush_comm_allreduce_f16(comm, part.data_ptr(), out.data_ptr(), n, stream), "allreduce")
+            assert torch.equal(out, part)
+        assert lib.wush_comm_allreduce_f16(comm, part.data_ptr(), out.data_ptr(), 12, stream) != 0       # not a multiple of 8
+        big = torch.zeros(256 * 1024, dtype=torch.float16, device="cuda")
+        assert lib.wush_comm_allreduce_f16(comm, big.data_ptr(), big.data_ptr(), big.numel(), stream) != 0  # larger than a slot
+        err = ctypes.c_int(-1)
+        capi.check(lib.wush_comm_error(comm, ctypes.byref(err)), "comm_error")
+        assert err.value == 0
+    finally:
+        capi.check(lib.wush_comm_destroy(comm), "comm_destroy")

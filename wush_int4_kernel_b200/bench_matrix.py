@@ -106,7 +106,7 @@ def measure_layer(layers: list, M: int, dev) -> dict:
     return line
 
 
-def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool) -> dict:
+def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None) -> dict:
     from . import _C, synth, timing
     from .linear import TensorParallelFFN, shard_bounds
 
@@ -119,6 +119,8 @@ def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool) -> dict:
         dn = synth.make_layer(il, hidden, seed=200 + 10 * c + rank, device=str(dev), quantiser=_C.quant_int4)
         ffn = TensorParallelFFN.from_local_shards((gu.t_bf16, gu.wq, gu.ws), (dn.t_bf16, dn.wq, dn.ws), tp, rank)
         ffn.down.reduce_output = distributed
+        if peer is not None:
+            ffn.use_peer_reduce(peer)
         blocks.append((ffn, gu))
     gen = torch.Generator(device=dev).manual_seed(9)
     x = synth.draw_activations(M, hidden, blocks[0][1].outliers, gen)
@@ -138,7 +140,9 @@ def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool) -> dict:
         t = float(tt.item())
     ops_total = 2.0 * M * hidden * (2 * inter) + 2.0 * M * inter * hidden
     wbytes = (2 * il * hidden + il * hidden) * 9 // 16
-    return {"block": "ffn 8192 -> 2 x 28672 -> 8192", "M": M, "tp": tp, "all_reduce": distributed, "graph": captured,
+    reduce_kind = "none" if not distributed else ("peer memory (one kernel)" if peer is not None and M * hidden <= peer.max_elements
+                                                  else "nccl fp32")
+    return {"block": "ffn 8192 -> 2 x 28672 -> 8192", "M": M, "tp": tp, "all_reduce": reduce_kind, "graph": captured,
             "us_per_block": round(t, 2), "eff_tops_whole_block": round(ops_total / t / 1e6, 2),
             "weight_bytes_per_rank": wbytes, "weight_stream_gbs_per_rank": round(wbytes / t / 1e3, 1)}
 
@@ -148,6 +152,7 @@ def main():
     ap.add_argument("--configs", default="qwen,llama,square,prefill")
     ap.add_argument("--tp", type=int, default=8, help="tensor-parallel degree emulated by `ffn` on one GPU")
     ap.add_argument("--ffn-rows", default="1,32,2048")
+    ap.add_argument("--nccl-only", action="store_true", help="finish the FFN block with the library all-reduce at every size")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -159,10 +164,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     from . import _C
     _C.init()
+    peer = None
+    if world > 1 and not args.nccl_only and "ffn" in args.configs.split(","):
+        from .peer_reduce import PeerAllReduce
+        peer = PeerAllReduce(max_elements=64 * 8192)           # decode-size results; larger ones go through NCCL
     for name in args.configs.split(","):
         if name == "ffn":
             for m in map(int, args.ffn_rows.split(",")):
-                line = measure_ffn(m, world if world > 1 else args.tp, rank if world > 1 else 0, dev, world > 1)
+                line = measure_ffn(m, world if world > 1 else args.tp, rank if world > 1 else 0, dev, world > 1, peer)
                 if rank == 0:
                     print(json.dumps(line), flush=True)
         elif world == 1:
@@ -172,6 +181,11 @@ def main():
                 print(json.dumps(measure_layer(layers, M, dev)), flush=True)
                 torch.cuda.empty_cache()
             del layers
+    if peer is not None:
+        err = peer.error()
+        peer.close()
+        if err:
+            raise SystemExit("peer all-reduce: a bounded wait ran out")
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

@@ -36,6 +36,12 @@ SIGNATURES = {
     "wush_group_partials": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "wush_quant_int4_tensor_scale": (_int, [_vp, _i64, _f32, _vp, _vp, _vp]),
     "wush_w4a4_gemm_tensor_scale": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "wush_comm_create": (_int, [_int, _int, _sz, ctypes.POINTER(ctypes.c_void_p)]),
+    "wush_comm_export": (_int, [_vp, _vp]),
+    "wush_comm_connect": (_int, [_vp, _int, _vp]),
+    "wush_comm_allreduce_f16": (_int, [_vp, _vp, _vp, _i64, _vp]),
+    "wush_comm_error": (_int, [_vp, ctypes.POINTER(_int)]),
+    "wush_comm_destroy": (_int, [_vp]),
     "wush_w4a4_gemm_tensor_scale_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "wush_w4a4_gemm_tensor_scale_ws": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _sz, _vp]),
 }

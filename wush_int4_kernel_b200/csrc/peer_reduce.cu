@@ -1,0 +1,267 @@
+// One-shot all-reduce (sum) of small fp16 partial products over NVLink peer memory
+// (C-ABI wush_comm_*).  No counterpart in the reference, which is single-GPU; this is the
+// exchange step of the row-parallel down projection when the FFN block is sharded over the
+// GPUs of one NVSwitch node.
+//
+// Decode-size results (M * N * 2 bytes: 16 KB .. a few MB) are latency-bound: a library
+// all-reduce costs tens of microseconds there, several times the sharded GEMV it follows.
+// Here every rank owns a buffer that all peers have mapped (CUDA IPC):
+//
+//   slots[2][slot_bytes]   this rank's partial result of step s lives in slot s & 1
+//   flags[world]           flags[r] = number of steps rank r has published
+//   state                  {step counter, arrival counters, error word}
+//
+// and one kernel per step does
+//   1. copy the local partial into this rank's slot (all CTAs, grid-stride), fence to system scope;
+//   2. the last CTA to finish the copy publishes: it stores step + 1 into flags[rank] of EVERY
+//      rank (remote stores with release semantics at system scope);
+//   3. every CTA polls its OWN flags (local memory) until all ranks have published this step
+//      -- bounded: after ~1 s it records an error and leaves;
+//   4. every CTA sums its share of the world's slots in rank order (peer loads that bypass L1),
+//      fp32 accumulation, and writes fp16; the last CTA to finish advances the step counter.
+// The result is bit-identical on all ranks (fixed summation order).  Two slots suffice: a rank
+// can only publish step s + 2 after its step s + 1 kernel has finished, which needed every
+// peer's step s + 1 flag, which a peer sends only after its own step s kernel -- the last reader
+// of slot s & 1 -- has completed.  All state lives in device memory, so the launch is the same
+// every step and can be captured in a CUDA Graph.
+//
+// The grid never exceeds the number of multiprocessors: every CTA must be resident while it waits.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace wush {
+namespace {
+
+constexpr int PR_MAX_WORLD = 16;
+constexpr int PR_THREADS = 256;
+constexpr uint32_t PR_POLL_LIMIT = 1u << 21;        // x ~0.5 us of back-off per poll
+
+struct CommState {                                   // device resident
+    unsigned int step;                               // steps completed so far
+    unsigned int copied;                             // CTAs that finished the copy of the current step
+    unsigned int done;                               // CTAs that finished the reduction of the current step
+    int error;                                       // 1 = a wait ran out
+};
+
+struct PeerTable {                                   // kernel argument: pointers of all ranks
+    const uint8_t* slots[PR_MAX_WORLD];              // base of rank r's two slots
+    unsigned int* flags[PR_MAX_WORLD];               // rank r's flag array
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {          // system-scope load, not served from L1
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(PR_THREADS)
+peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, long long n_vec,   // 8 halves per vector
+                          PeerTable peers, CommState* state, size_t slot_bytes, int rank, int world)
+{
+    __shared__ unsigned int s_step, s_ok;
+    pdl_wait();                                                        // the partial may come from the kernel just before
+    if (threadIdx.x == 0) s_step = *reinterpret_cast<volatile unsigned int*>(&state->step);
+    __syncthreads();
+    const unsigned int step = s_step;
+    const size_t slot_off = (size_t)(step & 1u) * slot_bytes;
+    const long long stride = (long long)gridDim.x * PR_THREADS;
+    const long long first = (long long)blockIdx.x * PR_THREADS + threadIdx.x;
+
+    // 1. publish the data
+    uint4* mine = reinterpret_cast<uint4*>(const_cast<uint8_t*>(peers.slots[rank]) + slot_off);
+    for (long long i = first; i < n_vec; i += stride) mine[i] = local[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int arrived = atomicAdd(&state->copied, 1u);
+        if (arrived == gridDim.x - 1) {
+            // 2. every CTA's part is written and fenced: tell everybody (this rank included)
+            __threadfence_system();
+            for (int r = 0; r < world; ++r) st_release_sys(peers.flags[r] + rank, step + 1u);
+        }
+        // 3. wait until every rank has published this step (flags only ever grow)
+        unsigned int ok = 1;
+        for (int r = 0; r < world && ok; ++r) {
+            uint32_t polls = 0;
+            while ((int)(ld_acquire_sys(peers.flags[rank] + r) - (step + 1u)) < 0) {
+                if (++polls > PR_POLL_LIMIT) { ok = 0; break; }
+                __nanosleep(polls < 64 ? 40 : 500);
+            }
+        }
+        if (!ok) atomicExch(&state->error, 1);
+        s_ok = ok;
+    }
+    __syncthreads();
+
+    // 4. reduce in rank order
+    if (s_ok) {
+        for (long long i = first; i < n_vec; i += stride) {
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+            for (int r = 0; r < world; ++r) {
+                const uint4 v = ld_peer_v4(reinterpret_cast<const uint4*>(peers.slots[r] + slot_off) + i);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[p]));
+                    acc[2 * p] += f.x;
+                    acc[2 * p + 1] += f.y;
+                }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                __half2 h = __floats2half2_rn(acc[2 * p], acc[2 * p + 1]);
+                o[p] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int finished = atomicAdd(&state->done, 1u);
+        if (finished == gridDim.x - 1) {                               // last CTA out: next step
+            state->copied = 0;
+            state->done = 0;
+            __threadfence();
+            state->step = step + 1u;
+        }
+    }
+}
+
+struct Comm {
+    int rank, world, device;
+    size_t slot_bytes;
+    uint8_t* base;                 // own allocation: slots | flags | state
+    uint8_t* peer_base[PR_MAX_WORLD];
+    bool connected[PR_MAX_WORLD];
+};
+
+constexpr size_t PR_FLAG_BYTES = 256, PR_STATE_BYTES = 256;
+
+size_t comm_bytes(size_t slot_bytes) { return 2 * slot_bytes + PR_FLAG_BYTES + PR_STATE_BYTES; }
+
+}  // namespace
+}  // namespace wush
+
+WUSH_API int wush_comm_create(int rank, int world, size_t slot_bytes, void** comm_out)
+{
+    using namespace wush;
+    if (int e = ensure_init()) return e;
+    WUSH_REQUIRE(comm_out, "comm_create: null pointer");
+    WUSH_REQUIRE(world >= 1 && world <= PR_MAX_WORLD && rank >= 0 && rank < world, "comm_create: bad rank %d of %d", rank, world);
+    WUSH_REQUIRE(slot_bytes > 0 && slot_bytes % 256 == 0, "comm_create: slot size must be a positive multiple of 256 bytes");
+    Comm* c = new Comm();
+    c->rank = rank;
+    c->world = world;
+    c->slot_bytes = slot_bytes;
+    cudaGetDevice(&c->device);
+    for (int r = 0; r < PR_MAX_WORLD; ++r) { c->peer_base[r] = nullptr; c->connected[r] = false; }
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), comm_bytes(slot_bytes));
+    if (e == cudaSuccess) e = cudaMemset(c->base, 0, comm_bytes(slot_bytes));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        delete c;
+        return fail(WUSH_ERR_CUDA, "comm_create: %s", cudaGetErrorString(e));
+    }
+    c->peer_base[rank] = c->base;
+    c->connected[rank] = true;
+    *comm_out = c;
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_export(void* comm, void* handle64)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm && handle64, "comm_export: null pointer");
+    Comm* c = static_cast<Comm*>(comm);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, c->base);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_export: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    memcpy(handle64, &h, 64);
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_connect(void* comm, int peer_rank, const void* handle64)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm && handle64, "comm_connect: null pointer");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(peer_rank >= 0 && peer_rank < c->world && peer_rank != c->rank, "comm_connect: bad peer rank %d", peer_rank);
+    WUSH_REQUIRE(!c->connected[peer_rank], "comm_connect: rank %d is already connected", peer_rank);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_connect: cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    c->peer_base[peer_rank] = static_cast<uint8_t*>(p);
+    c->connected[peer_rank] = true;
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_allreduce_f16(void* comm, const void* partial, void* out, int64_t n, void* stream)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm, "comm_allreduce: null communicator");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(n >= 0 && n % 8 == 0, "comm_allreduce: element count must be a multiple of 8");
+    if (n == 0) return WUSH_OK;
+    WUSH_REQUIRE(partial && out && aligned16(partial) && aligned16(out), "comm_allreduce: pointers must be 16-byte aligned");
+    WUSH_REQUIRE((size_t)n * 2 <= c->slot_bytes, "comm_allreduce: %lld halves do not fit the slot of %zu bytes", (long long)n,
+                 c->slot_bytes);
+    PeerTable t;
+    for (int r = 0; r < PR_MAX_WORLD; ++r) { t.slots[r] = nullptr; t.flags[r] = nullptr; }
+    for (int r = 0; r < c->world; ++r) {
+        WUSH_REQUIRE(c->connected[r], "comm_allreduce: rank %d is not connected", r);
+        t.slots[r] = c->peer_base[r];
+        t.flags[r] = reinterpret_cast<unsigned int*>(c->peer_base[r] + 2 * c->slot_bytes);
+    }
+    CommState* state = reinterpret_cast<CommState*>(c->base + 2 * c->slot_bytes + PR_FLAG_BYTES);
+    const long long n_vec = n / 8;
+    long long blocks = (n_vec + PR_THREADS - 1) / PR_THREADS;
+    if (blocks > sm_count()) blocks = sm_count();                       // every CTA resident while it waits
+    cudaError_t e = launch_dependent(peer_allreduce_f16_kernel, dim3((unsigned)blocks), dim3(PR_THREADS), (size_t)0,
+                                     (cudaStream_t)stream, (const uint4*)partial, (uint4*)out, n_vec, t, state, c->slot_bytes,
+                                     c->rank, c->world);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_allreduce launch: %s", cudaGetErrorString(e));
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_error(void* comm, int* error)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm && error, "comm_error: null pointer");
+    Comm* c = static_cast<Comm*>(comm);
+    CommState st;
+    cudaError_t e = cudaMemcpy(&st, c->base + 2 * c->slot_bytes + PR_FLAG_BYTES, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_error: %s", cudaGetErrorString(e));
+    *error = st.error;
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_destroy(void* comm)
+{
+    using namespace wush;
+    if (!comm) return WUSH_OK;
+    Comm* c = static_cast<Comm*>(comm);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < c->world; ++r)
+        if (r != c->rank && c->connected[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+    cudaFree(c->base);
+    delete c;
+    return WUSH_OK;
+}

@@ -118,9 +118,10 @@ class RowParallelW4A4Linear:
     matching transform blocks; ``__call__`` takes the local slice of the activations and
     returns the all-reduced product (fp16, summed in fp32)."""
 
-    def __init__(self, t, wq, ws, world: int, rank: int, group=None, reduce_output: bool = True):
+    def __init__(self, t, wq, ws, world: int, rank: int, group=None, reduce_output: bool = True, peer_reduce=None):
         K = wq.shape[1] * 2
         self.world, self.rank, self.group, self.reduce_output = world, rank, group, reduce_output
+        self.peer_reduce = peer_reduce          # optional peer_reduce.PeerAllReduce for decode-size results
         self.k0, self.k1 = shard_bounds(K, world, rank, 32)
         self.local = W4A4Linear(t[self.k0 // 32:self.k1 // 32].contiguous(),
                                 wq[:, self.k0 // 2:self.k1 // 2].contiguous(),
@@ -133,6 +134,9 @@ class RowParallelW4A4Linear:
         """All-reduce (sum in fp32) of this rank's partial product."""
         if not self.reduce_output or self.world == 1:
             return y
+        peer = getattr(self, "peer_reduce", None)
+        if peer is not None and peer.fits(y):
+            return peer(y)                      # one kernel over NVLink peer memory (same fp32 sum of the fp16 partials)
         import torch.distributed as dist
 
         acc = y.float()
@@ -154,6 +158,7 @@ class TensorParallelFFN:
         self.gate_up = W4A4Linear(t_gu, wq_gu[rows].contiguous(), ws_gu[rows].contiguous())
         self.down = RowParallelW4A4Linear.__new__(RowParallelW4A4Linear)
         self.down.world, self.down.rank, self.down.group, self.down.reduce_output = world, rank, group, True
+        self.down.peer_reduce = None
         self.down.k0, self.down.k1 = self.i0, self.i1
         self.down.local = W4A4Linear(t_d[self.i0 // 32:self.i1 // 32].contiguous(),
                                      wq_d[:, self.i0 // 2:self.i1 // 2].contiguous(),
@@ -167,6 +172,10 @@ class TensorParallelFFN:
         self = cls(gate_up, down, world=1, rank=0, group=group)
         self.down.world, self.down.rank = world, rank
         return self
+
+    def use_peer_reduce(self, peer_reduce) -> None:
+        """Finish small results with ``peer_reduce.PeerAllReduce`` instead of the library all-reduce."""
+        self.down.peer_reduce = peer_reduce
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         gu = self.gate_up(x)

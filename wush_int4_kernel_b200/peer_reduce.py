@@ -1,0 +1,67 @@
+"""One-shot all-reduce of small fp16 partial products over NVLink peer memory: the Python face of
+the ``wush_comm_*`` entry points (``csrc/peer_reduce.cu``).  The reference is single-GPU and has
+nothing like it; here it finishes the row-parallel down projection of the tensor-parallel FFN
+block at decode sizes, where a library all-reduce costs several times the sharded product.
+
+One process per GPU of ONE node.  Construction is collective over ``group`` (it exchanges CUDA IPC
+handles through ``torch.distributed``); calls are one kernel launch on the current stream and
+may be captured in a CUDA Graph.  Every rank must make the same sequence of calls.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import capi
+
+
+class PeerAllReduce:
+    def __init__(self, max_elements: int, group=None):
+        import torch.distributed as dist
+
+        self.lib = capi.load()
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.slot_bytes = (2 * max_elements + 255) // 256 * 256
+        self.max_elements = max_elements
+        comm = ctypes.c_void_p()
+        capi.check(self.lib.wush_comm_create(self.rank, self.world, self.slot_bytes, ctypes.byref(comm)), "comm_create")
+        self.comm = comm
+        handle = ctypes.create_string_buffer(64)
+        capi.check(self.lib.wush_comm_export(self.comm, handle), "comm_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        for r, h in enumerate(handles):
+            if r != self.rank:
+                capi.check(self.lib.wush_comm_connect(self.comm, r, ctypes.create_string_buffer(h, 64)), "comm_connect")
+        dist.barrier(group=group)                   # nobody publishes before everybody has mapped everybody
+
+    def fits(self, y: torch.Tensor) -> bool:
+        return (y.dtype == torch.float16 and y.is_cuda and y.is_contiguous() and y.numel() % 8 == 0
+                and y.numel() <= self.max_elements)
+
+    def __call__(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks (fp32 accumulation in rank order, fp16 result) of ``partial``."""
+        if not self.fits(partial):
+            raise ValueError("PeerAllReduce: needs a contiguous CUDA fp16 tensor of a multiple of 8 elements that fits the slot")
+        out = torch.empty_like(partial)
+        capi.check(self.lib.wush_comm_allreduce_f16(self.comm, partial.data_ptr(), out.data_ptr(), partial.numel(),
+                                                    torch.cuda.current_stream().cuda_stream), "comm_allreduce_f16")
+        return out
+
+    def error(self) -> int:
+        """1 if a bounded wait for a peer ever ran out on this rank (synchronises the device)."""
+        torch.cuda.synchronize()
+        e = ctypes.c_int(0)
+        capi.check(self.lib.wush_comm_error(self.comm, ctypes.byref(e)), "comm_error")
+        return int(e.value)
+
+    def close(self) -> None:
+        if self.comm is not None:
+            import torch.distributed as dist
+
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)          # no peer may still be reading this rank's slots
+            self.lib.wush_comm_destroy(self.comm)
+            self.comm = None
