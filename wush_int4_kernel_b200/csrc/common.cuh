@@ -63,6 +63,22 @@ __device__ __forceinline__ uint32_t code_exact(float x, float scale) {
     return (uint32_t)q & 0xFu;
 }
 
+// The same code, bit for bit, without a division on the common path.  `r_lo` / `r_hi` bracket
+// 1 / scale from below / above by a relative 2^-20 (the correctly rounded reciprocal times
+// 1 -+ 2^-20), so for either sign of x the real quotient and fl(x / scale) lie strictly between
+// x * r_lo and x * r_hi.  Adding 1.5 * 2^23 inside the FMA rounds each bound to the nearest-even
+// integer; rounding is monotonic, so when both bounds round to the same integer, fl(x / scale)
+// does too.  Otherwise (about 1.5e-5 of all elements, and every exact tie) the IEEE division
+// decides.  Returns the bits of 1.5 * 2^23 + code.
+__device__ __forceinline__ uint32_t code_bits_bracketed(float x, float scale, float r_lo, float r_hi) {
+    const float magic = 12582912.f;
+    float f = __fmaf_rn(x, r_lo, magic);
+    const float g = __fmaf_rn(x, r_hi, magic);
+    if (f != g) f = __fadd_rn(__fdiv_rn(x, scale), magic);
+    f = fminf(fmaxf(f, magic - 7.f), magic + 7.f);
+    return __float_as_uint(f);
+}
+
 // The whole bit-exact chain for one group held in registers.
 __device__ __forceinline__ void quant_group_exact(const float (&v)[32], uint4* packed, uint32_t* scale_bits) {
     float s1 = 0.f, s2 = 0.f;
@@ -73,13 +89,17 @@ __device__ __forceinline__ void quant_group_exact(const float (&v)[32], uint4* p
     }
     float scale;
     *scale_bits = sigma_clip_scale(s1, s2, &scale);
+    const float r = __frcp_rn(scale);
+    const float r_lo = __fmul_rn(r, 1.0f - 9.5367431640625e-7f), r_hi = __fmul_rn(r, 1.0f + 9.5367431640625e-7f);   // 2^-20
     uint32_t w[4];
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
+        // bits = bits(magic) + code exactly, so sum_e bits_e * 16^e (mod 2^32) is the word of the offset
+        // nibbles code + 8 plus a constant: one multiply-add per element, constant off, bit 3 flipped back
         uint32_t acc = 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc |= code_exact(v[b * 8 + e], scale) << (4 * e);
-        w[b] = acc;
+        for (int e = 0; e < 8; ++e) acc = code_bits_bracketed(v[b * 8 + e], scale, r_lo, r_hi) * (1u << (4 * e)) + acc;
+        w[b] = (acc - (0x4B400000u - 8u) * 0x11111111u) ^ 0x88888888u;
     }
     *packed = make_uint4(w[0], w[1], w[2], w[3]);
 }
