@@ -193,11 +193,19 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
  *                      2n <= slot_bytes; every rank must call it the same number of times with the
  *                      same n.  One kernel launch, no host synchronisation, capturable; a rank waits for
  *                      its peers inside the kernel for about a second at most, then records an error;
+ *   wush_comm_connect_pointer  the same for a peer buffer of THIS process (wush_comm_base of another
+ *                      communicator on a device with peer access): emulation of several ranks in one
+ *                      process, and tests;
+ *   wush_comm_set_poll_limit   bound of the in-kernel wait, in polls of about half a microsecond
+ *                      (default 2^21, about a second);
  *   wush_comm_error    (synchronous) 1 if a wait ever ran out on this rank;
  *   wush_comm_destroy  unmaps and frees. */
 int wush_comm_create(int rank, int world, size_t slot_bytes, void** comm);
 int wush_comm_export(void* comm, void* handle64);
 int wush_comm_connect(void* comm, int peer_rank, const void* handle64);
+int wush_comm_connect_pointer(void* comm, int peer_rank, void* peer_base);
+int wush_comm_base(void* comm, void** base);
+int wush_comm_set_poll_limit(void* comm, unsigned int polls);
 int wush_comm_allreduce_f16(void* comm, const void* partial, void* out, int64_t n, void* stream);
 int wush_comm_error(void* comm, int* error);
 int wush_comm_destroy(void* comm);

@@ -39,6 +39,9 @@ SIGNATURES = {
     "wush_comm_create": (_int, [_int, _int, _sz, ctypes.POINTER(ctypes.c_void_p)]),
     "wush_comm_export": (_int, [_vp, _vp]),
     "wush_comm_connect": (_int, [_vp, _int, _vp]),
+    "wush_comm_connect_pointer": (_int, [_vp, _int, _vp]),
+    "wush_comm_base": (_int, [_vp, ctypes.POINTER(ctypes.c_void_p)]),
+    "wush_comm_set_poll_limit": (_int, [_vp, ctypes.c_uint]),
     "wush_comm_allreduce_f16": (_int, [_vp, _vp, _vp, _i64, _vp]),
     "wush_comm_error": (_int, [_vp, ctypes.POINTER(_int)]),
     "wush_comm_destroy": (_int, [_vp]),

@@ -163,8 +163,15 @@ fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict
     pdl_launch_dependents();                              // the consumer may get resident; it waits before reading q/s
     const int warps = blockDim.x >> 5;
     const int g = blockIdx.x * warps + (threadIdx.x >> 5);
-    if (g >= C) return;                                   // whole warp leaves together
     const int lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    // This kernel may itself have been launched early (programmatic dependent of the kernel that
+    // produces x): pull the T block towards L2 meanwhile, read nothing before the wait.
+    if (g < C) {
+        const uint8_t* tb = reinterpret_cast<const uint8_t*>(t + (size_t)g * 1024);
+        if (lane < 16) prefetch_l2(tb + lane * 128);
+    }
+    pdl_wait();
+    if (g >= C) return;                                   // whole warp leaves together
     const long long r_begin = (long long)blockIdx.y * rows_per_cta;
     const long long r_end = min(rows, r_begin + rows_per_cta);
 
@@ -227,9 +234,10 @@ static int launch_fast(const void* x, const void* t, int64_t rows, int64_t C, ui
     const int64_t gy = (rows + rows_per_cta - 1) / rows_per_cta;
     WUSH_REQUIRE(gy <= 65535, "fused_tq: too many rows");
     dim3 grid((unsigned)((C + warps - 1) / warps), (unsigned)gy);
-    fused_tq_fast_kernel<SILU><<<grid, warps * 32, 0, st>>>(x, (const __nv_bfloat16*)t, (uint32_t*)q, (__nv_bfloat16*)s,
-                                                            (long long)rows, (int)C, rows_per_cta);
-    return check_launch("fused_tq_fast");
+    cudaError_t e = launch_dependent(fused_tq_fast_kernel<SILU>, grid, dim3(warps * 32), (size_t)0, st, x, (const __nv_bfloat16*)t,
+                                     (uint32_t*)q, (__nv_bfloat16*)s, (long long)rows, (int)C, rows_per_cta);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "fused_tq_fast launch: %s", cudaGetErrorString(e));
+    return WUSH_OK;
 }
 
 }  // namespace wush

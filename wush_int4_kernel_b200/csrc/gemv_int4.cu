@@ -116,6 +116,7 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
         sxf[idx] = __bfloat162float(xs[idx]) * (1.0f / 256.0f);
     }
     __syncthreads();
+    pdl_launch_dependents();            // a dependent may become resident as this grid drains; it waits before reading y
 
     for (; unit < units; unit += stride) {
         float acc[R][MB];

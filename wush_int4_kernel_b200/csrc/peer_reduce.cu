@@ -26,6 +26,7 @@
 // every step and can be captured in a CUDA Graph.
 //
 // The grid never exceeds the number of multiprocessors: every CTA must be resident while it waits.
+#include <cstddef>
 #include <cstring>
 
 #include "common.cuh"
@@ -33,15 +34,16 @@
 namespace wush {
 namespace {
 
-constexpr int PR_MAX_WORLD = 16;
+constexpr int PR_MAX_WORLD = 8;                     // the GPUs of one NVSwitch node
 constexpr int PR_THREADS = 256;
-constexpr uint32_t PR_POLL_LIMIT = 1u << 21;        // x ~0.5 us of back-off per poll
+constexpr uint32_t PR_POLL_LIMIT = 1u << 21;        // default bound of a wait: x ~0.5 us of back-off per poll
 
 struct CommState {                                   // device resident
     unsigned int step;                               // steps completed so far
     unsigned int copied;                             // CTAs that finished the copy of the current step
     unsigned int done;                               // CTAs that finished the reduction of the current step
     int error;                                       // 1 = a wait ran out
+    unsigned int poll_limit;                         // polls after which a wait gives up
 };
 
 struct PeerTable {                                   // kernel argument: pointers of all ranks
@@ -75,6 +77,7 @@ peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ o
     if (threadIdx.x == 0) s_step = *reinterpret_cast<volatile unsigned int*>(&state->step);
     __syncthreads();
     const unsigned int step = s_step;
+    const unsigned int poll_limit = *reinterpret_cast<volatile unsigned int*>(&state->poll_limit);
     const size_t slot_off = (size_t)(step & 1u) * slot_bytes;
     const long long stride = (long long)gridDim.x * PR_THREADS;
     const long long first = (long long)blockIdx.x * PR_THREADS + threadIdx.x;
@@ -84,41 +87,55 @@ peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ o
     for (long long i = first; i < n_vec; i += stride) mine[i] = local[i];
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int arrived = atomicAdd(&state->copied, 1u);
+    if (threadIdx.x < 32) {
+        // warp 0: lane r talks to rank r, so the remote stores and the polls of all ranks overlap
+        const int lane = threadIdx.x;
+        unsigned int arrived = 0;
+        if (lane == 0) arrived = atomicAdd(&state->copied, 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
         if (arrived == gridDim.x - 1) {
             // 2. every CTA's part is written and fenced: tell everybody (this rank included)
             __threadfence_system();
-            for (int r = 0; r < world; ++r) st_release_sys(peers.flags[r] + rank, step + 1u);
+            if (lane < world) st_release_sys(peers.flags[lane] + rank, step + 1u);
         }
         // 3. wait until every rank has published this step (flags only ever grow)
-        unsigned int ok = 1;
-        for (int r = 0; r < world && ok; ++r) {
+        bool ok = true;
+        if (lane < world) {
             uint32_t polls = 0;
-            while ((int)(ld_acquire_sys(peers.flags[rank] + r) - (step + 1u)) < 0) {
-                if (++polls > PR_POLL_LIMIT) { ok = 0; break; }
-                __nanosleep(polls < 64 ? 40 : 500);
+            while ((int)(ld_acquire_sys(peers.flags[rank] + lane) - (step + 1u)) < 0) {
+                if (++polls > poll_limit) { ok = false; break; }
+                __nanosleep(polls < 64 ? 20 : 500);
             }
         }
-        if (!ok) atomicExch(&state->error, 1);
-        s_ok = ok;
+        ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) {
+            if (!ok) atomicExch(&state->error, 1);
+            s_ok = ok ? 1u : 0u;
+        }
     }
     __syncthreads();
 
     // 4. reduce in rank order
     if (s_ok) {
         for (long long i = first; i < n_vec; i += stride) {
+            // all peers' vectors are requested before the first one is used: one NVLink round trip, not `world`
+            uint4 v[PR_MAX_WORLD];
+#pragma unroll
+            for (int r = 0; r < PR_MAX_WORLD; ++r)             // ranks beyond the world re-read this rank's slot (ignored below)
+                v[r] = ld_peer_v4(reinterpret_cast<const uint4*>(peers.slots[r < world ? r : rank] + slot_off) + i);
             float acc[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-            for (int r = 0; r < world; ++r) {
-                const uint4 v = ld_peer_v4(reinterpret_cast<const uint4*>(peers.slots[r] + slot_off) + i);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[p]));
-                    acc[2 * p] += f.x;
-                    acc[2 * p + 1] += f.y;
+            for (int r = 0; r < PR_MAX_WORLD; ++r) {
+                if (r < world) {
+                    const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[p]));
+                        acc[2 * p] += f.x;
+                        acc[2 * p + 1] += f.y;
+                    }
                 }
             }
             uint32_t o[4];
@@ -148,6 +165,7 @@ struct Comm {
     uint8_t* base;                 // own allocation: slots | flags | state
     uint8_t* peer_base[PR_MAX_WORLD];
     bool connected[PR_MAX_WORLD];
+    bool borrowed[PR_MAX_WORLD];   // mapped by pointer (same process), not through an IPC handle
 };
 
 constexpr size_t PR_FLAG_BYTES = 256, PR_STATE_BYTES = 256;
@@ -169,9 +187,13 @@ WUSH_API int wush_comm_create(int rank, int world, size_t slot_bytes, void** com
     c->world = world;
     c->slot_bytes = slot_bytes;
     cudaGetDevice(&c->device);
-    for (int r = 0; r < PR_MAX_WORLD; ++r) { c->peer_base[r] = nullptr; c->connected[r] = false; }
+    for (int r = 0; r < PR_MAX_WORLD; ++r) { c->peer_base[r] = nullptr; c->connected[r] = false; c->borrowed[r] = false; }
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), comm_bytes(slot_bytes));
     if (e == cudaSuccess) e = cudaMemset(c->base, 0, comm_bytes(slot_bytes));
+    if (e == cudaSuccess) {
+        CommState init = {0, 0, 0, 0, PR_POLL_LIMIT};
+        e = cudaMemcpy(c->base + 2 * slot_bytes + PR_FLAG_BYTES, &init, sizeof(init), cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         delete c;
@@ -210,6 +232,38 @@ WUSH_API int wush_comm_connect(void* comm, int peer_rank, const void* handle64)
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_connect: cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
     c->peer_base[peer_rank] = static_cast<uint8_t*>(p);
     c->connected[peer_rank] = true;
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_connect_pointer(void* comm, int peer_rank, void* peer_base)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm && peer_base, "comm_connect_pointer: null pointer");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(peer_rank >= 0 && peer_rank < c->world && peer_rank != c->rank, "comm_connect_pointer: bad peer rank %d", peer_rank);
+    WUSH_REQUIRE(!c->connected[peer_rank], "comm_connect_pointer: rank %d is already connected", peer_rank);
+    c->peer_base[peer_rank] = static_cast<uint8_t*>(peer_base);
+    c->connected[peer_rank] = true;
+    c->borrowed[peer_rank] = true;
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_base(void* comm, void** base)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm && base, "comm_base: null pointer");
+    *base = static_cast<Comm*>(comm)->base;
+    return WUSH_OK;
+}
+
+WUSH_API int wush_comm_set_poll_limit(void* comm, unsigned int polls)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm && polls > 0, "comm_set_poll_limit: bad argument");
+    Comm* c = static_cast<Comm*>(comm);
+    cudaError_t e = cudaMemcpy(c->base + 2 * c->slot_bytes + PR_FLAG_BYTES + offsetof(CommState, poll_limit), &polls,
+                               sizeof(polls), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_set_poll_limit: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
 
@@ -260,7 +314,7 @@ WUSH_API int wush_comm_destroy(void* comm)
     Comm* c = static_cast<Comm*>(comm);
     cudaDeviceSynchronize();
     for (int r = 0; r < c->world; ++r)
-        if (r != c->rank && c->connected[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+        if (r != c->rank && c->connected[r] && !c->borrowed[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
     cudaFree(c->base);
     delete c;
     return WUSH_OK;
