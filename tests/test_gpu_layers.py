@@ -144,3 +144,33 @@ def test_peer_allreduce_single_rank():
         assert err.value == 0
     finally:
         capi.check(lib.wush_comm_destroy(comm), "comm_destroy")
+
+
+def test_peer_allreduce_wait_runs_out():
+    """Failure detection without a fault: rank 0 of a world of two whose peer never publishes.
+    The peer's buffer is a second communicator of this process that never runs; the wait of the
+    kernel is bounded (set to ~2 ms here), it records the error word and returns, and the
+    context stays usable."""
+    import ctypes
+    from wush_int4_kernel_b200 import capi
+    lib = capi.load()
+    mine, other = ctypes.c_void_p(), ctypes.c_void_p()
+    capi.check(lib.wush_comm_create(0, 2, 64 * 1024, ctypes.byref(mine)), "comm_create")
+    capi.check(lib.wush_comm_create(1, 2, 64 * 1024, ctypes.byref(other)), "comm_create")
+    try:
+        base = ctypes.c_void_p()
+        capi.check(lib.wush_comm_base(other, ctypes.byref(base)), "comm_base")
+        capi.check(lib.wush_comm_connect_pointer(mine, 1, base), "comm_connect_pointer")
+        capi.check(lib.wush_comm_set_poll_limit(mine, 4096), "comm_set_poll_limit")
+        part = torch.ones(4096, dtype=torch.float16, device="cuda")
+        out = torch.zeros_like(part)
+        stream = torch.cuda.current_stream().cuda_stream
+        capi.check(lib.wush_comm_allreduce_f16(mine, part.data_ptr(), out.data_ptr(), part.numel(), stream), "allreduce")
+        torch.cuda.synchronize()                                  # returns: nothing hangs
+        err = ctypes.c_int(0)
+        capi.check(lib.wush_comm_error(mine, ctypes.byref(err)), "comm_error")
+        assert err.value == 1
+        assert float((part * 2).sum().item()) == 8192.0           # the device still computes
+    finally:
+        capi.check(lib.wush_comm_destroy(mine), "comm_destroy")
+        capi.check(lib.wush_comm_destroy(other), "comm_destroy")
