@@ -185,7 +185,7 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
  * No counterpart in the reference (single GPU).  The row-parallel down projection of a
  * tensor-parallel FFN block ends in a sum over ranks; at decode sizes a library all-reduce costs
  * several times the sharded product.  One process per GPU of one node:
- *   wush_comm_create   allocates this rank's exchange buffer (two slots of slot_bytes, flags, state).
+ *   wush_comm_create   allocates this rank's exchange buffer (2 x world slots of slot_bytes, flags, state).
  *                      The ONLY call of this library that allocates device memory; set-up time.
  *   wush_comm_export   64-byte CUDA IPC handle of that buffer, to be sent to every other rank;
  *   wush_comm_connect  maps a peer's buffer from its handle (once per peer);
@@ -193,6 +193,12 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
  *                      2n <= slot_bytes; every rank must call it the same number of times with the
  *                      same n.  One kernel launch, no host synchronisation, capturable; a rank waits for
  *                      its peers inside the kernel for about a second at most, then records an error;
+ *   wush_comm_gemv_allreduce   decode product (M <= 2, the operands of wush_w4a4_gemm) AND the sum over
+ *                      ranks: the product kernel's epilogue stores its fp16 result into every rank's
+ *                      buffer over NVLink and its last CTA publishes the step; the reduction then reads
+ *                      local memory only.  WUSH_ERR_UNSUPPORTED for other shapes (use wush_w4a4_gemm +
+ *                      wush_comm_allreduce_f16).  Same calling discipline as wush_comm_allreduce_f16, and
+ *                      the two may be mixed step by step;
  *   wush_comm_connect_pointer  the same for a peer buffer of THIS process (wush_comm_base of another
  *                      communicator on a device with peer access): emulation of several ranks in one
  *                      process, and tests;
@@ -207,6 +213,8 @@ int wush_comm_connect_pointer(void* comm, int peer_rank, void* peer_base);
 int wush_comm_base(void* comm, void** base);
 int wush_comm_set_poll_limit(void* comm, unsigned int polls);
 int wush_comm_allreduce_f16(void* comm, const void* partial, void* out, int64_t n, void* stream);
+int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq,
+                             const void* ws, int64_t M, int64_t N, int64_t K, void* out, void* stream);
 int wush_comm_error(void* comm, int* error);
 int wush_comm_destroy(void* comm);
 

@@ -57,6 +57,17 @@ def main():
     torch.cuda.synchronize()
     assert torch.equal(out, warm), "graph replay differs from the eager call"
     assert peer.error() == 0
+    # fused product + exchange (decode rows): equals product followed by the pull all-reduce, bit for bit
+    from wush_int4_kernel_b200.linear import quantise_activations, w4a4_product
+    for rows in (1, 2, 1):
+        xr = synth.draw_activations(rows, 1024, layer.outliers, gen)[:, k0:k1].contiguous()
+        shard = RowParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, reduce_output=False)
+        xq_l, xs_l = quantise_activations(xr, shard.local.t)
+        fused = peer.product_allreduce(xq_l, xs_l, shard.local.wq, shard.local.ws)
+        assert fused is not None
+        plain = peer(w4a4_product(xq_l, xs_l, shard.local.wq, shard.local.ws))
+        assert torch.equal(fused, plain), f"pushed product differs at rows={rows}"
+    assert peer.error() == 0
     row2 = RowParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, peer_reduce=peer)
     y2 = row2(x[:, k0:k1].contiguous())
     assert ((y2.float() - full.float()).norm() / full.float().norm()).item() <= 2e-3

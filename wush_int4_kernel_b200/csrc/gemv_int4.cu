@@ -27,6 +27,7 @@
 // reads the activations only after griddepcontrol.wait.
 // Algorithmic HBM bytes per call: 9*N*K/16 (codes + scales of W) + 9*M*K/16 + 2*M*N.
 #include "common.cuh"
+#include "peer_common.cuh"
 
 namespace wush {
 
@@ -69,14 +70,17 @@ __device__ __forceinline__ void issue_unit_loads(RowLoads& r, const uint8_t* __r
 
 // R = weight rows per warp and trip.  R > 1 is used when a row has at most 32 * (8/R) groups,
 // so that short rows still put 8 loads per lane in flight; a trip is then a whole unit.
-template <int MB, int R>
+// PUSH: instead of y the result goes into slot (step & 1, rank) of EVERY rank's exchange buffer
+// (remote stores over NVLink from the epilogue); when the last CTA is done it publishes the step
+// to all ranks.  The sum over ranks is then a purely local read (peer_reduce.cu).
+template <int MB, int R, bool PUSH>
 __global__ void __launch_bounds__(GV_MAX_WARPS * 32)
 gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
                  const __nv_bfloat16* __restrict__ xs,     // (MB, G)
                  const uint8_t* __restrict__ wq,           // (N, K/2)
                  const __nv_bfloat16* __restrict__ ws,     // (N, G)
-                 __half* __restrict__ y,                   // (MB, N)
-                 int N, int K)
+                 __half* __restrict__ y,                   // (MB, N); unused with PUSH
+                 int N, int K, const PeerTable peers)
 {
     constexpr int U = 8 / R;
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -117,6 +121,12 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
     }
     __syncthreads();
     pdl_launch_dependents();            // a dependent may become resident as this grid drains; it waits before reading y
+    unsigned int step = 0;
+    size_t push_off = 0;
+    if constexpr (PUSH) {               // the step counter is stable: the reduction of the previous step has completed
+        step = *reinterpret_cast<volatile unsigned int*>(&peers.state->step);
+        push_off = slot_offset(peers, step, peers.rank);
+    }
 
     for (; unit < units; unit += stride) {
         float acc[R][MB];
@@ -160,10 +170,23 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
                 const int n = unit * R + r;
                 if (n < N) {
 #pragma unroll
-                    for (int m = 0; m < MB; ++m) y[(size_t)m * N + n] = __float2half_rn(acc[r][m]);
+                    for (int m = 0; m < MB; ++m) {
+                        const __half h = __float2half_rn(acc[r][m]);
+                        if constexpr (PUSH) {
+                            for (int p = 0; p < peers.world; ++p)
+                                reinterpret_cast<__half*>(peers.base[p] + push_off)[(size_t)m * N + n] = h;
+                        } else {
+                            y[(size_t)m * N + n] = h;
+                        }
+                    }
                 }
             }
         }
+    }
+    if constexpr (PUSH) {
+        __threadfence_system();                            // this thread's remote stores are ordered before the flag
+        __syncthreads();
+        if (threadIdx.x < 32) comm_count_and_publish(peers, step, threadIdx.x);
     }
 }
 
@@ -174,7 +197,7 @@ size_t gemv_smem_bytes(int M, int64_t K) { return (size_t)M * (K / 32) * (16 + 1
 // costs a full memory latency at a fraction of the bandwidth).
 struct GemvShape { int warps, ctas_per_sm; };
 
-template <int MB, int R>
+template <int MB, int R, bool PUSH>
 static GemvShape pick_shape(size_t smem, long long units)
 {
     struct Cache { size_t smem; int per_sm[GV_MAX_WARPS + 1]; };
@@ -182,7 +205,7 @@ static GemvShape pick_shape(size_t smem, long long units)
     if (cache.smem != smem) {
         for (int w = 4; w <= GV_MAX_WARPS; ++w) {
             int q = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_dp4a_kernel<MB, R>, w * 32, smem) != cudaSuccess) q = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_dp4a_kernel<MB, R, PUSH>, w * 32, smem) != cudaSuccess) q = 0;
             cache.per_sm[w] = q;
         }
         cache.smem = smem;
@@ -211,9 +234,9 @@ static GemvShape pick_shape(size_t smem, long long units)
     return best;
 }
 
-template <int MB, int R>
+template <int MB, int R, bool PUSH>
 static int launch_gemv(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t N,
-                       int64_t K, void* y, cudaStream_t st)
+                       int64_t K, void* y, const PeerTable& peers, cudaStream_t st)
 {
     const size_t smem = gemv_smem_bytes(MB, K);
     const long long units = (N + R - 1) / R;
@@ -222,24 +245,27 @@ static int launch_gemv(const uint8_t* xq, const void* xs, const uint8_t* wq, con
     static thread_local size_t last_smem = 0;
     static thread_local GemvShape shape = {8, 1};
     if (last_units != units || last_smem != smem) {
-        shape = pick_shape<MB, R>(smem, units);
+        shape = pick_shape<MB, R, PUSH>(smem, units);
         last_units = units;
         last_smem = smem;
     }
     long long ctas = (long long)sm_count() * shape.ctas_per_sm;
     const long long needed = (units + shape.warps - 1) / shape.warps;
     if (ctas > needed) ctas = needed;
-    cudaError_t e = launch_dependent(gemv_dp4a_kernel<MB, R>, dim3((unsigned)ctas), dim3(shape.warps * 32), smem, st,
+    cudaError_t e = launch_dependent(gemv_dp4a_kernel<MB, R, PUSH>, dim3((unsigned)ctas), dim3(shape.warps * 32), smem, st,
                                      (const uint32_t*)xq, (const __nv_bfloat16*)xs, wq, (const __nv_bfloat16*)ws, (__half*)y,
-                                     (int)N, (int)K);
+                                     (int)N, (int)K, peers);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "gemv launch: %s", cudaGetErrorString(e));
-    return check_launch("gemv_dp4a");
+    return WUSH_OK;
 }
 
 template <int MB, int R>
 static cudaError_t set_attr()
 {
-    return cudaFuncSetAttribute(gemv_dp4a_kernel<MB, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemv_dp4a_kernel<MB, R, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess && MB <= 2)
+        e = cudaFuncSetAttribute(gemv_dp4a_kernel<MB, R, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    return e;
 }
 
 int gemv_set_attributes()
@@ -253,29 +279,41 @@ int gemv_set_attributes()
     return WUSH_OK;
 }
 
-template <int MB>
+template <int MB, bool PUSH>
 static int launch_rows(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t N, int64_t K,
-                       void* y, cudaStream_t st)
+                       void* y, const PeerTable& peers, cudaStream_t st)
 {
     const int64_t slots = (K / 32 + 31) / 32;              // 16-byte loads per lane and row
     if constexpr (MB <= 2) {
-        if (slots <= 2) return launch_gemv<MB, 4>(xq, xs, wq, ws, N, K, y, st);
+        if (slots <= 2) return launch_gemv<MB, 4, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
     }
-    if (slots <= 4) return launch_gemv<MB, 2>(xq, xs, wq, ws, N, K, y, st);
-    return launch_gemv<MB, 1>(xq, xs, wq, ws, N, K, y, st);
+    if (slots <= 4) return launch_gemv<MB, 2, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
+    return launch_gemv<MB, 1, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
 }
 
 // M in 1..4, shared memory must fit (checked by the dispatcher).
 int gemv_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N,
                   int64_t K, void* y, cudaStream_t st)
 {
+    const PeerTable none = {};
     switch (M) {
-        case 1: return launch_rows<1>(xq, xs, wq, ws, N, K, y, st);
-        case 2: return launch_rows<2>(xq, xs, wq, ws, N, K, y, st);
-        case 3: return launch_rows<3>(xq, xs, wq, ws, N, K, y, st);
-        case 4: return launch_rows<4>(xq, xs, wq, ws, N, K, y, st);
+        case 1: return launch_rows<1, false>(xq, xs, wq, ws, N, K, y, none, st);
+        case 2: return launch_rows<2, false>(xq, xs, wq, ws, N, K, y, none, st);
+        case 3: return launch_rows<3, false>(xq, xs, wq, ws, N, K, y, none, st);
+        case 4: return launch_rows<4, false>(xq, xs, wq, ws, N, K, y, none, st);
     }
     return fail(WUSH_ERR_INVALID_ARGUMENT, "gemv: M=%lld outside 1..4", (long long)M);
+}
+
+// The same product with its result pushed into the exchange buffers of all ranks (M <= 2).
+int gemv_dispatch_push(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N,
+                       int64_t K, const PeerTable& peers, cudaStream_t st)
+{
+    switch (M) {
+        case 1: return launch_rows<1, true>(xq, xs, wq, ws, N, K, nullptr, peers, st);
+        case 2: return launch_rows<2, true>(xq, xs, wq, ws, N, K, nullptr, peers, st);
+    }
+    return fail(WUSH_ERR_UNSUPPORTED, "gemv(push): M=%lld outside 1..2", (long long)M);
 }
 
 }  // namespace wush

@@ -7,9 +7,9 @@
 // all-reduce costs tens of microseconds there, several times the sharded GEMV it follows.
 // Here every rank owns a buffer that all peers have mapped (CUDA IPC):
 //
-//   slots[2][slot_bytes]   this rank's partial result of step s lives in slot s & 1
-//   flags[world]           flags[r] = number of steps rank r has published
-//   state                  {step counter, arrival counters, error word}
+//   slots[2][world][slot_bytes]   slot (s & 1, r) holds rank r's partial result of step s
+//   flags[world]                  flags[r] = number of steps rank r has published
+//   state                         {step counter, arrival counters, error word, wait bound}
 //
 // and one kernel per step does
 //   1. copy the local partial into this rank's slot (all CTAs, grid-stride), fence to system scope;
@@ -26,78 +26,50 @@
 // every step and can be captured in a CUDA Graph.
 //
 // The grid never exceeds the number of multiprocessors: every CTA must be resident while it waits.
+//
+// Pushed form (wush_comm_gemv_allreduce): the decode GEMV writes its result straight into slot
+// (s & 1, rank) of EVERY rank's buffer from its epilogue and publishes when its last CTA is done;
+// the kernel here then skips steps 1 and 2 and sums the slots of its OWN buffer -- no copy, and no
+// NVLink round trip after the flags have arrived.
 #include <cstddef>
 #include <cstring>
 
 #include "common.cuh"
+#include "peer_common.cuh"
 
 namespace wush {
 namespace {
 
-constexpr int PR_MAX_WORLD = 8;                     // the GPUs of one NVSwitch node
 constexpr int PR_THREADS = 256;
 constexpr uint32_t PR_POLL_LIMIT = 1u << 21;        // default bound of a wait: x ~0.5 us of back-off per poll
 
-struct CommState {                                   // device resident
-    unsigned int step;                               // steps completed so far
-    unsigned int copied;                             // CTAs that finished the copy of the current step
-    unsigned int done;                               // CTAs that finished the reduction of the current step
-    int error;                                       // 1 = a wait ran out
-    unsigned int poll_limit;                         // polls after which a wait gives up
-};
-
-struct PeerTable {                                   // kernel argument: pointers of all ranks
-    const uint8_t* slots[PR_MAX_WORLD];              // base of rank r's two slots
-    unsigned int* flags[PR_MAX_WORLD];               // rank r's flag array
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {          // system-scope load, not served from L1
-    uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p)
-                 : "memory");
-    return v;
-}
-
 __global__ void __launch_bounds__(PR_THREADS)
 peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, long long n_vec,   // 8 halves per vector
-                          PeerTable peers, CommState* state, size_t slot_bytes, int rank, int world)
+                          const PeerTable peers, int pushed)
 {
     __shared__ unsigned int s_step, s_ok;
+    CommState* state = peers.state;
+    const int rank = peers.rank, world = peers.world;
     pdl_wait();                                                        // the partial may come from the kernel just before
     if (threadIdx.x == 0) s_step = *reinterpret_cast<volatile unsigned int*>(&state->step);
     __syncthreads();
     const unsigned int step = s_step;
     const unsigned int poll_limit = *reinterpret_cast<volatile unsigned int*>(&state->poll_limit);
-    const size_t slot_off = (size_t)(step & 1u) * slot_bytes;
     const long long stride = (long long)gridDim.x * PR_THREADS;
     const long long first = (long long)blockIdx.x * PR_THREADS + threadIdx.x;
 
-    // 1. publish the data
-    uint4* mine = reinterpret_cast<uint4*>(const_cast<uint8_t*>(peers.slots[rank]) + slot_off);
-    for (long long i = first; i < n_vec; i += stride) mine[i] = local[i];
-    __threadfence_system();
+    if (!pushed) {
+        // 1. publish the data: this rank's slot of its own buffer
+        uint4* mine = reinterpret_cast<uint4*>(peers.base[rank] + slot_offset(peers, step, rank));
+        for (long long i = first; i < n_vec; i += stride) mine[i] = local[i];
+        __threadfence_system();
+    }
     __syncthreads();
     if (threadIdx.x < 32) {
         // warp 0: lane r talks to rank r, so the remote stores and the polls of all ranks overlap
         const int lane = threadIdx.x;
-        unsigned int arrived = 0;
-        if (lane == 0) arrived = atomicAdd(&state->copied, 1u);
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        if (arrived == gridDim.x - 1) {
-            // 2. every CTA's part is written and fenced: tell everybody (this rank included)
-            __threadfence_system();
-            if (lane < world) st_release_sys(peers.flags[lane] + rank, step + 1u);
-        }
+        // 2. every CTA's part is written and fenced: the last one tells everybody (this rank included)
+        if (!pushed) comm_count_and_publish(peers, step, lane);
         // 3. wait until every rank has published this step (flags only ever grow)
         bool ok = true;
         if (lane < world) {
@@ -121,8 +93,10 @@ peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ o
             // all peers' vectors are requested before the first one is used: one NVLink round trip, not `world`
             uint4 v[PR_MAX_WORLD];
 #pragma unroll
-            for (int r = 0; r < PR_MAX_WORLD; ++r)             // ranks beyond the world re-read this rank's slot (ignored below)
-                v[r] = ld_peer_v4(reinterpret_cast<const uint4*>(peers.slots[r < world ? r : rank] + slot_off) + i);
+            for (int r = 0; r < PR_MAX_WORLD; ++r) {           // ranks beyond the world re-read this rank's slot (ignored below)
+                const int src = r < world ? r : rank;
+                v[r] = ld_sys_v4(reinterpret_cast<const uint4*>(peers.base[pushed ? rank : src] + slot_offset(peers, step, src)) + i);
+            }
             float acc[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] = 0.f;
@@ -168,9 +142,34 @@ struct Comm {
     bool borrowed[PR_MAX_WORLD];   // mapped by pointer (same process), not through an IPC handle
 };
 
-constexpr size_t PR_FLAG_BYTES = 256, PR_STATE_BYTES = 256;
+size_t slots_bytes(const Comm* c) { return 2 * (size_t)c->world * c->slot_bytes; }
+size_t comm_bytes(const Comm* c) { return slots_bytes(c) + PR_FLAG_BYTES + PR_STATE_BYTES; }
 
-size_t comm_bytes(size_t slot_bytes) { return 2 * slot_bytes + PR_FLAG_BYTES + PR_STATE_BYTES; }
+int fill_table(const Comm* c, PeerTable* t, const char* what)
+{
+    for (int r = 0; r < PR_MAX_WORLD; ++r) { t->base[r] = nullptr; t->flags[r] = nullptr; }
+    for (int r = 0; r < c->world; ++r) {
+        if (!c->connected[r]) return fail(WUSH_ERR_INVALID_ARGUMENT, "%s: rank %d is not connected", what, r);
+        t->base[r] = c->peer_base[r];
+        t->flags[r] = reinterpret_cast<unsigned int*>(c->peer_base[r] + slots_bytes(c));
+    }
+    t->state = reinterpret_cast<CommState*>(c->base + slots_bytes(c) + PR_FLAG_BYTES);
+    t->slot_bytes = c->slot_bytes;
+    t->rank = c->rank;
+    t->world = c->world;
+    return WUSH_OK;
+}
+
+int launch_reduce(const Comm* c, const PeerTable& t, const void* partial, void* out, int64_t n, int pushed, cudaStream_t st)
+{
+    const long long n_vec = n / 8;
+    long long blocks = (n_vec + PR_THREADS - 1) / PR_THREADS;
+    if (blocks > sm_count()) blocks = sm_count();                       // every CTA resident while it waits
+    cudaError_t e = launch_dependent(peer_allreduce_f16_kernel, dim3((unsigned)blocks), dim3(PR_THREADS), (size_t)0, st,
+                                     (const uint4*)partial, (uint4*)out, n_vec, t, pushed);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_allreduce launch: %s", cudaGetErrorString(e));
+    return WUSH_OK;
+}
 
 }  // namespace
 }  // namespace wush
@@ -188,11 +187,11 @@ WUSH_API int wush_comm_create(int rank, int world, size_t slot_bytes, void** com
     c->slot_bytes = slot_bytes;
     cudaGetDevice(&c->device);
     for (int r = 0; r < PR_MAX_WORLD; ++r) { c->peer_base[r] = nullptr; c->connected[r] = false; c->borrowed[r] = false; }
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), comm_bytes(slot_bytes));
-    if (e == cudaSuccess) e = cudaMemset(c->base, 0, comm_bytes(slot_bytes));
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), comm_bytes(c));
+    if (e == cudaSuccess) e = cudaMemset(c->base, 0, comm_bytes(c));
     if (e == cudaSuccess) {
         CommState init = {0, 0, 0, 0, PR_POLL_LIMIT};
-        e = cudaMemcpy(c->base + 2 * slot_bytes + PR_FLAG_BYTES, &init, sizeof(init), cudaMemcpyHostToDevice);
+        e = cudaMemcpy(c->base + slots_bytes(c) + PR_FLAG_BYTES, &init, sizeof(init), cudaMemcpyHostToDevice);
     }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
@@ -261,7 +260,7 @@ WUSH_API int wush_comm_set_poll_limit(void* comm, unsigned int polls)
     using namespace wush;
     WUSH_REQUIRE(comm && polls > 0, "comm_set_poll_limit: bad argument");
     Comm* c = static_cast<Comm*>(comm);
-    cudaError_t e = cudaMemcpy(c->base + 2 * c->slot_bytes + PR_FLAG_BYTES + offsetof(CommState, poll_limit), &polls,
+    cudaError_t e = cudaMemcpy(c->base + slots_bytes(c) + PR_FLAG_BYTES + offsetof(CommState, poll_limit), &polls,
                                sizeof(polls), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_set_poll_limit: %s", cudaGetErrorString(e));
     return WUSH_OK;
@@ -278,21 +277,36 @@ WUSH_API int wush_comm_allreduce_f16(void* comm, const void* partial, void* out,
     WUSH_REQUIRE((size_t)n * 2 <= c->slot_bytes, "comm_allreduce: %lld halves do not fit the slot of %zu bytes", (long long)n,
                  c->slot_bytes);
     PeerTable t;
-    for (int r = 0; r < PR_MAX_WORLD; ++r) { t.slots[r] = nullptr; t.flags[r] = nullptr; }
-    for (int r = 0; r < c->world; ++r) {
-        WUSH_REQUIRE(c->connected[r], "comm_allreduce: rank %d is not connected", r);
-        t.slots[r] = c->peer_base[r];
-        t.flags[r] = reinterpret_cast<unsigned int*>(c->peer_base[r] + 2 * c->slot_bytes);
-    }
-    CommState* state = reinterpret_cast<CommState*>(c->base + 2 * c->slot_bytes + PR_FLAG_BYTES);
-    const long long n_vec = n / 8;
-    long long blocks = (n_vec + PR_THREADS - 1) / PR_THREADS;
-    if (blocks > sm_count()) blocks = sm_count();                       // every CTA resident while it waits
-    cudaError_t e = launch_dependent(peer_allreduce_f16_kernel, dim3((unsigned)blocks), dim3(PR_THREADS), (size_t)0,
-                                     (cudaStream_t)stream, (const uint4*)partial, (uint4*)out, n_vec, t, state, c->slot_bytes,
-                                     c->rank, c->world);
-    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_allreduce launch: %s", cudaGetErrorString(e));
-    return WUSH_OK;
+    if (int s = fill_table(c, &t, "comm_allreduce")) return s;
+    return launch_reduce(c, t, partial, out, n, 0, (cudaStream_t)stream);
+}
+
+// Product of the decode GEMV and the sum over ranks as one chain of two kernels that share the
+// exchange: the GEMV's epilogue stores into every rank's slot, its last CTA publishes, the
+// reduction reads only local memory.  WUSH_ERR_UNSUPPORTED for shapes the GEMV does not take
+// (M > 2, huge K) or results that do not fit a slot: use wush_w4a4_gemm + wush_comm_allreduce_f16.
+namespace wush {
+int gemv_dispatch_push(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, const PeerTable&,
+                       cudaStream_t);
+size_t gemv_smem_bytes(int M, int64_t K);
+}
+
+WUSH_API int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws,
+                                      int64_t M, int64_t N, int64_t K, void* out, void* stream)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm, "comm_gemv_allreduce: null communicator");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(M >= 1 && N >= 1 && K > 0 && K % 32 == 0, "comm_gemv_allreduce: bad shape");
+    WUSH_REQUIRE(xq && xs && wq && ws && out, "comm_gemv_allreduce: null pointer");
+    WUSH_REQUIRE(aligned16(xq) && aligned16(wq) && aligned16(out), "comm_gemv_allreduce: pointers must be 16-byte aligned");
+    if (M > 2 || (M * N) % 8 != 0 || (size_t)(M * N) * 2 > c->slot_bytes || gemv_smem_bytes((int)M, K) > 200 * 1024)
+        return fail(WUSH_ERR_UNSUPPORTED, "comm_gemv_allreduce: M=%lld N=%lld K=%lld is outside the pushed GEMV's range",
+                    (long long)M, (long long)N, (long long)K);
+    PeerTable t;
+    if (int s = fill_table(c, &t, "comm_gemv_allreduce")) return s;
+    if (int s = gemv_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream)) return s;
+    return launch_reduce(c, t, nullptr, out, M * N, 1, (cudaStream_t)stream);
 }
 
 WUSH_API int wush_comm_error(void* comm, int* error)
@@ -301,7 +315,7 @@ WUSH_API int wush_comm_error(void* comm, int* error)
     WUSH_REQUIRE(comm && error, "comm_error: null pointer");
     Comm* c = static_cast<Comm*>(comm);
     CommState st;
-    cudaError_t e = cudaMemcpy(&st, c->base + 2 * c->slot_bytes + PR_FLAG_BYTES, sizeof(st), cudaMemcpyDeviceToHost);
+    cudaError_t e = cudaMemcpy(&st, c->base + slots_bytes(c) + PR_FLAG_BYTES, sizeof(st), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_error: %s", cudaGetErrorString(e));
     *error = st.error;
     return WUSH_OK;

@@ -128,7 +128,19 @@ class RowParallelW4A4Linear:
                                 ws[:, self.k0 // 32:self.k1 // 32].contiguous())
 
     def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
-        return self.reduce(self.local(x_local))
+        lead = x_local.shape[:-1]
+        xq, xs = quantise_activations(x_local.reshape(-1, x_local.shape[-1]), self.local.t)
+        return self.product_and_reduce(xq, xs).reshape(*lead, self.local.out_features)
+
+    def product_and_reduce(self, xq: torch.Tensor, xs: torch.Tensor) -> torch.Tensor:
+        """Local product of already quantised activations, then the sum over ranks; at most two
+        rows with a peer communicator attached run as the fused product + exchange chain."""
+        peer = getattr(self, "peer_reduce", None)
+        if peer is not None and self.reduce_output and self.world > 1:
+            y = peer.product_allreduce(xq, xs, self.local.wq, self.local.ws)
+            if y is not None:
+                return y
+        return self.reduce(w4a4_product(xq, xs, self.local.wq, self.local.ws))
 
     def reduce(self, y: torch.Tensor) -> torch.Tensor:
         """All-reduce (sum in fp32) of this rank's partial product."""
@@ -182,8 +194,7 @@ class TensorParallelFFN:
         # SiLU(gate) * up -> bf16 -> transform -> quantise in one kernel: h never goes to HBM
         lead = gu.shape[:-1]
         hq, hs = _ops().fused_silu_mul_transform_quant_int4(gu.reshape(-1, gu.shape[-1]), self.down.local.t)
-        y = w4a4_product(hq, hs, self.down.local.wq, self.down.local.ws).reshape(*lead, self.down.local.out_features)
-        return self.down.reduce(y)
+        return self.down.product_and_reduce(hq, hs).reshape(*lead, self.down.local.out_features)
 
     def reference_call(self, x: torch.Tensor) -> torch.Tensor:
         """The same block as a composition of the single ops (separate activation kernels)."""

@@ -50,6 +50,20 @@ class PeerAllReduce:
                                                     torch.cuda.current_stream().cuda_stream), "comm_allreduce_f16")
         return out
 
+    def product_allreduce(self, xq, xs, wq, ws):
+        """Decode product (at most two activation rows) and the sum over ranks in one chain: the
+        product kernel pushes its result into every rank's buffer.  Returns ``None`` for shapes
+        outside that kernel's range (the caller then uses the product op followed by ``__call__``)."""
+        K = wq.shape[1] * 2
+        rows, n = xq.numel() // (K // 2), wq.shape[0]
+        if rows > 2 or (rows * n) % 8 or rows * n > self.max_elements or rows * (K // 32) * 36 > 200 * 1024:
+            return None
+        out = torch.empty(rows, n, dtype=torch.float16, device=xq.device)
+        capi.check(self.lib.wush_comm_gemv_allreduce(self.comm, xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(),
+                                                     rows, n, K, out.data_ptr(), torch.cuda.current_stream().cuda_stream),
+                   "comm_gemv_allreduce")
+        return out
+
     def error(self) -> int:
         """1 if a bounded wait for a peer ever ran out on this rank (synchronises the device)."""
         torch.cuda.synchronize()
