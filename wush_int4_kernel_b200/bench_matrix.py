@@ -140,8 +140,12 @@ def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None) -
         t = float(tt.item())
     ops_total = 2.0 * M * hidden * (2 * inter) + 2.0 * M * inter * hidden
     wbytes = (2 * il * hidden + il * hidden) * 9 // 16
-    reduce_kind = "none" if not distributed else ("peer memory (one kernel)" if peer is not None and M * hidden <= peer.max_elements
-                                                  else "nccl fp32")
+    if not distributed:
+        reduce_kind = "none"
+    elif peer is None or M * hidden > peer.max_elements:
+        reduce_kind = "nccl fp32"
+    else:
+        reduce_kind = "peer memory, pushed from the product kernel" if M <= 2 else "peer memory, one kernel"
     return {"block": "ffn 8192 -> 2 x 28672 -> 8192", "M": M, "tp": tp, "all_reduce": reduce_kind, "graph": captured,
             "us_per_block": round(t, 2), "eff_tops_whole_block": round(ops_total / t / 1e6, 2),
             "weight_bytes_per_rank": wbytes, "weight_stream_gbs_per_rank": round(wbytes / t / 1e3, 1)}
