@@ -75,6 +75,17 @@ def cpu_layer_inputs(M: int, n_rows: int, seed: int = 0):
     return x, t, wq, ws
 
 
+def cpu_model() -> str:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def time_cpu_layer(M: int, n_rows: int, steps: int, warmup: int):
     from oracle import w4a4_oracle as orc
     cores = os.cpu_count() or 1
@@ -105,7 +116,7 @@ def run_reference_arm(args):
         "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4", "data": "synthetic",
         "config": {"workload": f"llama70b_gate_up_decode K={K_DIM} N={N_DIM} M={M}", "K": K_DIM, "N": N_DIM, "M": M},
-        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "cpu": cpu_model(), "kind": "port",
                          "sample": f"whole layer (N={n_rows} rows of W), {len(times)} steps, OpenMP over output columns"},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -285,7 +296,7 @@ def run_gpu_arm(args):
         n_rep = int(max(3, min(2000, 12.0 / max(first[0], 1e-3))))
         times, cores = time_cpu_layer(M, N_DIM, n_rep, 0)
         med = statistics.median(times)
-        cpu = {"value": 2.0 * M * N_DIM * K_DIM / med / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+        cpu = {"value": 2.0 * M * N_DIM * K_DIM / med / 1e12, "unit": "TOPS", "cores": cores, "cpu": cpu_model(), "kind": "port",
                "sample": f"whole layer M={M}, median of {n_rep} calls ({time.perf_counter() - t0:.1f} s of CPU work)",
                "us_per_step": med * 1e6}
 
