@@ -93,12 +93,16 @@ def test_two_process_nccl_if_available():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import os
+    import socket
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    with socket.socket() as sock:                      # a port nobody is using right now
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", os.path.join(root, "tests", "nccl_worker.py")]
+           "127.0.0.1", "--master-port", str(port), os.path.join(root, "tests", "nccl_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "rank 0 ok" in out.stdout and "rank 1 ok" in out.stdout
