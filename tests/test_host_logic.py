@@ -146,3 +146,28 @@ def test_synthetic_layer_is_seeded():
     assert not torch.equal(a.wq, c.wq)
     assert a.wq.shape == (64, 128) and a.ws.shape == (64, 8) and a.t_bf16.shape == (8, 32, 32)
     assert len(a.outliers) == max(1, round(0.005 * 256))
+
+
+def test_block_compat_matches_reference_call_sites():
+    """The stand-ins for the external `block_transform` / `compute_gram` modules, exercised the way the
+    reference's tests/test_sw1.py:14-38 does: product invariance < 1e-9 and the two routes to W T^-1 agree."""
+    import torch
+    from wush_int4_kernel_b200 import block_compat as bt, wush_transform as wt
+    gen = torch.Generator().manual_seed(0)
+    M, N, K = 256, 128, 128
+    X = torch.randn(M, K, dtype=torch.float64, generator=gen)
+    W = torch.randn(N, K, dtype=torch.float64, generator=gen)
+    X[:, 5::32] *= 15.0
+    W[:, 12::32] *= 8.0
+    hi = torch.float64
+    T = bt.get_wush_transform(gram_weight=bt.get_diag_block_gram(x=W, size=32, dtype=hi) / N,
+                              gram_activation=bt.get_diag_block_gram(x=X, size=32, dtype=hi) / M,
+                              use_hadamard=True, high_dtype=hi, round_dtype=hi)
+    assert torch.equal(T, wt.compute_wush_transform(X, W, group_size=32))
+    T_w = bt.get_inversed_transposed_transform(T, high_dtype=hi, round_dtype=hi)
+    Wa = bt.apply_block_transform(x=W, transform=T, is_inverse_transpose=True)
+    Wb = bt.apply_block_transform(x=W, transform=T_w, is_inverse_transpose=False)
+    assert torch.allclose(Wa, Wb, rtol=1e-9, atol=1e-9)
+    Xp = bt.apply_block_transform(x=X, transform=T, is_inverse_transpose=False)
+    Y = X @ W.t()
+    assert ((Xp @ Wa.t() - Y).norm() / Y.norm()).item() < 1e-9
