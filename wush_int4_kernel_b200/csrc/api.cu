@@ -103,9 +103,14 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
 {
     if (variant != WUSH_GEMM_AUTO) return variant;
     const bool gemv_ok = gemv_smem_bytes((int)(M < 4 ? M : 4), K) <= 200 * 1024;
-    if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0)) return WUSH_GEMM_GEMV;
+    // three or four rows: the tensor-core streaming kernel wins on wide layers, the CUDA-core GEMV on narrow
+    // ones (a CTA of the streaming kernel is left with one or two warps there)
+    if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0 || N <= 16384)) return WUSH_GEMM_GEMV;
     if (M <= 32) return WUSH_GEMM_DECODE;
     if (M >= 128 && f16_supported(M, N, K)) return WUSH_GEMM_TILE_F16;
+    // 32 < M < 128: the streaming kernel in blocks of 32 rows (measured 2 x faster at M = 64 than a
+    // half-empty 128-row tile); the exact tile kernel where the streaming kernel does not take K
+    if (K % 256 == 0) return WUSH_GEMM_DECODE;
     return tc_supported(M, N, K) ? WUSH_GEMM_TILE : WUSH_GEMM_DECODE;
 }
 
