@@ -25,6 +25,7 @@
 // Algorithmic traffic: the pre-pass reads 9/16 B and writes 2 B per operand element; the GEMM
 // reads fp16 operands (L2-resident across the M tiles that share a weight tile).
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -37,6 +38,9 @@ namespace {
 // ------------------------------------------------------------------------------------------------
 // pre-pass
 // ------------------------------------------------------------------------------------------------
+// PERM: inside every octet of codes the output order is 0,4,1,5,2,6,3,7 -- the order in which the
+// fused kernel below produces the other operand (a sum over k does not care, as long as both agree).
+template <bool PERM>
 __global__ void __launch_bounds__(256)
 dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ s, __half* __restrict__ out,
                    float* __restrict__ row_factor, long long rows, int K)
@@ -67,8 +71,10 @@ dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restric
         for (int i = 0; i < 4; ++i) {
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                const int lo = ((int)(ww[i] << (28 - 8 * p))) >> 28;           // nibble 2p, sign extended
-                const int hi = ((int)(ww[i] << (24 - 8 * p))) >> 28;           // nibble 2p + 1
+                const int lo = PERM ? ((int)(ww[i] << (28 - 4 * p))) >> 28      // nibble p
+                                    : ((int)(ww[i] << (28 - 8 * p))) >> 28;    // nibble 2p, sign extended
+                const int hi = PERM ? ((int)(ww[i] << (12 - 4 * p))) >> 28      // nibble p + 4
+                                    : ((int)(ww[i] << (24 - 8 * p))) >> 28;    // nibble 2p + 1
                 __half2 h = __floats2half2_rn((float)lo * sc, (float)hi * sc);  // exact products
                 ow[i * 4 + p] = *reinterpret_cast<uint32_t*>(&h);
             }
@@ -276,6 +282,249 @@ gemm_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 1) tc::tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same product with the weights widened INSIDE the kernel (M up to a few thousand rows)
+// ------------------------------------------------------------------------------------------------
+// The pre-pass over the weights above costs a read of the packed matrix, a write of four times
+// as many bytes and their re-read by the GEMM: more than the GEMM itself below M ~ 1000.  Here
+// only the activations are widened beforehand; the weight tile arrives packed (TMA, 32 bytes per
+// row and stage) and eight warps turn it into the fp16 B operand in shared memory, in exactly the
+// 128-byte-swizzled K-major layout a TMA load of fp16 would have produced:
+//   nibble -> fp16: (w ^ 0x88888888) puts code + 8 into every nibble; (x >> 4j) & 0x000F000F |
+//   0x64006400 is the half2 (1024 + code_j + 8, 1024 + code_{j+4} + 8); minus 1032 gives the codes,
+//   times the row-shifted scale gives code * scale, both exact in fp16.
+// The octet order 0,4,1,5,2,6,3,7 that falls out is mirrored by the activation pre-pass.
+//   warp 0      TMA: fp16 activation tile (128 x 64) + packed weight tile (256 rows x 32 B) per stage
+//   warp 1      tcgen05.mma issue (as above)
+//   warps 4-7   epilogue (as above)
+//   warps 8-23  widening: thread (d, g) owns group g (32 codes) of weight row d of the tile in every stage
+constexpr int Q_STAGES = 5;                                       // ring of TMA stages: activation tile + packed weight tile
+constexpr int Q_BUFS = 3;                                         // ring of widened (fp16) weight tiles
+constexpr int Q_THREADS = 768;
+constexpr int QA_BYTES = FM * 128, QB_BYTES = FN * 128, QP_BYTES = FN * 32;
+constexpr int Q_STAGE = QA_BYTES + QP_BYTES;                     // 24 KB
+constexpr int Q_BOFF = Q_STAGES * Q_STAGE;                       // widened tiles after the TMA ring (1 KB aligned)
+constexpr int Q_BARS = Q_BOFF + Q_BUFS * QB_BYTES;
+constexpr int Q_TOTAL = Q_BARS + (2 * Q_STAGES + 2 * Q_BUFS + 2 * F_ACC + 1) * 8 + 16 + 1024;
+
+// one word of eight nibbles -> eight fp16 (code * scale), octet order 0,4,1,5,2,6,3,7
+__device__ __forceinline__ uint4 widen_word_f16(uint32_t w, __half2 s2) {
+    const uint32_t x = w ^ 0x88888888u;
+    const __half2 off = __half2half2(__ushort_as_half((unsigned short)0x6408));        // 1032
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t h = ((x >> (4 * j)) & 0x000F000Fu) | 0x64006400u;
+        __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&h), off), s2);
+        o[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// per weight row: 2^e (for the epilogue) and 2^-e (for the widening), e = exponent of its largest scale
+__global__ void __launch_bounds__(256)
+row_shift_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ up, float* __restrict__ down, long long rows, int G)
+{
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const unsigned short* sr = reinterpret_cast<const unsigned short*>(s) + row * G;
+    unsigned mx = 0;
+    for (int g = lane; g < G; g += 32) mx = max(mx, (unsigned)(sr[g] & 0x7fffu));
+#pragma unroll
+    for (int off = 16; off; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    int e = (int)(mx >> 7) - 127;
+    e = max(-100, min(100, e));
+    if (lane == 0) {
+        up[row] = __uint_as_float((uint32_t)(127 + e) << 23);
+        down[row] = __uint_as_float((uint32_t)(127 - e) << 23);
+    }
+}
+
+__global__ void __launch_bounds__(Q_THREADS, 1)
+gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
+                      const unsigned short* __restrict__ ws, const float* __restrict__ down, const TileScale sc,
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + Q_BARS);     // TMA stage landed
+    uint64_t* empty = full + Q_STAGES;                               // TMA stage consumed: MMA (A) + 16 widening warps (packed B)
+    uint64_t* widened = empty + Q_STAGES;                            // fp16 weight tile written
+    uint64_t* bfree = widened + Q_BUFS;                              // fp16 weight tile consumed by the MMA
+    uint64_t* acc_full = bfree + Q_BUFS;
+    uint64_t* acc_empty = acc_full + F_ACC;
+    uint64_t* done_bar = acc_empty + F_ACC;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_m = (M + FM - 1) / FM, tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
+    const int k_steps = K / 64, G = K >> 5;
+
+    if (tid == 0) {
+        for (int i = 0; i < Q_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 17); }
+        for (int i = 0; i < Q_BUFS; ++i) { tc::mbar_init(&widened[i], 16); tc::mbar_init(&bfree[i], 1); }
+        for (int i = 0; i < F_ACC; ++i) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 4); }
+        tc::mbar_init(done_bar, 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, 512);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(&map_p);
+            uint32_t slot = 0, phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
+                    uint8_t* st = smem + slot * Q_STAGE;
+                    tc::mbar_expect_tx(&full[slot], QA_BYTES + QP_BYTES);
+                    tc::tma_load_2d(st, &map_a, &full[slot], ks * 64, m0);
+                    tc::tma_load_2d(st + QA_BYTES, &map_p, &full[slot], ks * 32, n0);
+                    ++issued;
+                    if (++slot == Q_STAGES) { slot = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                atomicExch(err, 1);
+                for (int i = 0; i < (issued < Q_STAGES ? issued : Q_STAGES); ++i)
+                    for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                        if (tc::mbar_try_wait(&full[i], 0) || tc::mbar_try_wait(&full[i], 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 0, buf = 0, bphase = 0, ab = 0, aphase = 0;
+            const uint32_t idesc = tc::idesc_f16(FN);
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (!tc::mbar_wait(&acc_empty[ab], aphase ^ 1)) { ok = false; break; }
+                tc::tc_fence_after();
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!tc::mbar_wait(&full[slot], phase) || !tc::mbar_wait(&widened[buf], bphase)) { ok = false; break; }
+                    tc::tc_fence_after();
+                    const uint32_t sa = tc::smem_u32(smem + slot * Q_STAGE), sb = tc::smem_u32(smem + Q_BOFF + buf * QB_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        mma_f16(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
+                                (ks | kk) ? 1u : 0u);
+                    tc::mma_commit(&empty[slot]);                              // the activation tile of this stage
+                    tc::mma_commit(&bfree[buf]);                               // and the widened weight tile are free again
+                    if (++slot == Q_STAGES) { slot = 0; phase ^= 1; }
+                    if (++buf == Q_BUFS) { buf = 0; bphase ^= 1; }
+                }
+                if (!ok) break;
+                tc::mma_commit(&acc_full[ab]);
+                if (++ab == F_ACC) { ab = 0; aphase ^= 1; }
+            }
+            if (!ok) atomicExch(err, 2);
+            tc::mma_commit(done_bar);
+            for (uint32_t spin = 0; spin < WUSH_SPIN_LIMIT; ++spin)
+                if (tc::mbar_try_wait(done_bar, 0)) break;
+        }
+    } else if (warp >= 8) {
+        // ------------------------------ widening warps -------------------------------------------
+        const int d = (tid - 256) & 255, g = (tid - 256) >> 8;     // weight row of the tile, group of the stage
+        uint32_t slot = 0, phase = 0, buf = 0, bphase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const int n = (t / tiles_m) * FN + d;
+            const bool live = n < N;
+            const float dn = live ? down[n] : 0.f;
+            // scales: one 16-byte load covers this row's 8 groups = 4 stages; the next one is in flight meanwhile
+            const uint4* srow = reinterpret_cast<const uint4*>(ws + (size_t)(live ? n : 0) * G);
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            uint4 s_cur = zero4, s_nxt = live ? __ldg(srow) : zero4;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                if ((ks & 3) == 0) {
+                    s_cur = s_nxt;
+                    if (live && ks + 4 < k_steps) s_nxt = __ldg(srow + (ks >> 2) + 1);
+                }
+                const uint32_t pair = (ks & 2) ? ((ks & 1) ? s_cur.w : s_cur.z) : ((ks & 1) ? s_cur.y : s_cur.x);   // groups 2ks, 2ks+1
+                const float s_f = g ? bf16_hi(pair) : bf16_lo(pair);
+                if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
+                const uint4 w = *reinterpret_cast<const uint4*>(smem + slot * Q_STAGE + QA_BYTES + d * 32 + g * 16);
+                const __half2 s2 = __float2half2_rn(__fmul_rn(s_f, dn));                           // exact shift
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                uint4 o[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[c] = widen_word_f16(ww[c], s2);
+                __syncwarp();                                      // the packed words of this warp are in registers
+                if (lane == 0) tc::mbar_arrive(&empty[slot]);
+                if (!tc::mbar_wait(&bfree[buf], bphase ^ 1)) { ok = false; break; }
+                uint8_t* brow = smem + Q_BOFF + buf * QB_BYTES + d * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(brow + (((g * 4 + c) ^ (d & 7)) << 4)) = o[c];
+                tc::fence_proxy_async();                           // generic-proxy writes -> visible to tcgen05.mma
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&widened[buf]);
+                if (++slot == Q_STAGES) { slot = 0; phase ^= 1; }
+                if (++buf == Q_BUFS) { buf = 0; bphase ^= 1; }
+            }
+        }
+        if (!ok && lane == 0) atomicExch(err, 8);
+    } else if (warp >= 4) {
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        uint32_t ab = 0, aphase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
+            if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
+            tc::tc_fence_after();
+            const int m = m0 + row;
+            const float fm = (m < M) ? sc.fa[m] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < FN / 32; ++c) {
+                uint32_t v[32];
+                tc::tmem_ld32(tmem + lane_base + ab * FN + c * 32, v);
+                tc::tmem_ld_wait();
+                if (c == FN / 32 - 1) {
+                    tc::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive(&acc_empty[ab]);
+                }
+                const int n = n0 + c * 32;
+                if (m < M && n < N) {
+                    __half* yr = y + (size_t)m * N + n;
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        if (n + v8 * 8 + 8 <= N) {
+                            const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
+                            const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
+                            const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                            uint32_t o[4];
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
+                                                              __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
+                                o[p] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                }
+            }
+            if (++ab == F_ACC) { ab = 0; aphase ^= 1; }
+        }
+        if (!ok && lane == 0) atomicExch(err, 4);
+    }
+
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem, 512);
+}
+
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 }  // namespace
@@ -285,6 +534,7 @@ int f16_set_attributes()
     if (int s = resolve_tensor_map_encoder()) return s;
     cudaError_t e = cudaFuncSetAttribute(gemm_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_TOTAL);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "tile GEMM: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
@@ -292,10 +542,43 @@ int f16_set_attributes()
 // K in whole 64-element stages, 16-byte output vectors and factor vectors.
 bool f16_supported(int64_t M, int64_t N, int64_t K) { return M >= 1 && K % 64 == 0 && N % 8 == 0; }
 
-// scratch: error word | fp16 activations (M x K) | fp16 weights (N x K) | 2^e per row of each
+// Rows up to which the weights are widened inside the GEMM (no fp16 copy of W in the scratch).  Measured at
+// K = 8192, N = 57344: 217 vs 464 us at M = 128, 410 vs 529 us at M = 256, equal at M = 512, slower beyond.
+constexpr int64_t FUSED_MAX_ROWS = 384;
+static bool use_fused(int64_t M, int64_t N, int64_t K) { return M <= FUSED_MAX_ROWS && K % 256 == 0; }   // whole 16-byte scale vectors
+
+// scratch: error word | fp16 activations (M x K) | [fp16 weights (N x K), unless widened in-kernel] |
+// 2^e per row of each | 2^-e per weight row
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
-    return 256 + align256((size_t)M * K * 2) + align256((size_t)N * K * 2) + align256((size_t)M * 4) + align256((size_t)N * 4);
+    const size_t w16 = use_fused(M, N, K) ? 0 : align256((size_t)N * K * 2);
+    return 256 + align256((size_t)M * K * 2) + w16 + align256((size_t)M * 4) + 2 * align256((size_t)N * 4);
+}
+
+static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N,
+                              int64_t K, void* y, void* workspace, cudaStream_t st)
+{
+    uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+    int* err = reinterpret_cast<int*>(base);
+    __half* a16 = reinterpret_cast<__half*>(base + 256);
+    float* fa = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + align256((size_t)M * K * 2));
+    float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
+    float* dn = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fb) + align256((size_t)N * 4));
+    cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    dequant_f16_kernel<true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
+    row_shift_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)ws, fb, dn, (long long)N, (int)(K / 32));
+    if (int s = check_launch("f16 pre-pass")) return s;
+    CUtensorMap ma, mp;
+    int s;
+    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    if ((s = make_map_2d(&mp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 32, FN, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
+    const int64_t tiles = ((M + FM - 1) / FM) * ((N + FN - 1) / FN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const TileScale sc = {fa, fb, 0.f, nullptr};
+    gemm_f16_fused_kernel<<<grid, Q_THREADS, Q_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N,
+                                                            (int)K, err);
+    return check_launch("gemm_f16_fused");
 }
 
 int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
@@ -306,6 +589,8 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     if (workspace_bytes < f16_workspace_bytes(M, N, K))
         return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, %zu given",
                     f16_workspace_bytes(M, N, K), workspace_bytes);
+    if (use_fused(M, N, K) && aligned16(ws))
+        return f16_fused_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, st);
     uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
     int* err = reinterpret_cast<int*>(base);
     __half* a16 = reinterpret_cast<__half*>(base + 256);
@@ -314,8 +599,8 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
     cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
-    dequant_f16_kernel<<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
-    dequant_f16_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
+    dequant_f16_kernel<false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
+    dequant_f16_kernel<false><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
     if (int s = check_launch("dequant_f16")) return s;
     CUtensorMap ma, mb;
     int s;
