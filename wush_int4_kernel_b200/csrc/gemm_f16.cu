@@ -525,6 +525,206 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (warp == 1) tc::tmem_dealloc(tmem, 512);
 }
 
+// The same kernel on 256 x 256 tiles: every widened weight tile feeds TWO MMAs (activation rows 0-127 and
+// 128-255, accumulators in TMEM columns 0-255 and 256-511), which doubles the instruction budget of the
+// widening warps per MMA cycle.  The two accumulators fill the whole TMEM, so a tile's epilogue (eight warps)
+// does not overlap the next tile's MMAs.
+constexpr int R_STAGES = 3, R_BUFS = 3;
+constexpr int R_THREADS = 896;                                    // + warps 24-27: epilogue of the upper 128 rows
+constexpr int RA_BYTES = 2 * FM * 128;
+constexpr int R_STAGE = RA_BYTES + QP_BYTES;                     // 40 KB
+constexpr int R_BOFF = R_STAGES * R_STAGE;
+constexpr int R_BARS = R_BOFF + R_BUFS * QB_BYTES;
+constexpr int R_TOTAL = R_BARS + (2 * R_STAGES + 2 * R_BUFS + 2 * F_ACC + 1) * 8 + 16 + 1024;
+
+__global__ void __launch_bounds__(R_THREADS, 1)
+gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
+                      const unsigned short* __restrict__ ws, const float* __restrict__ down, const TileScale sc,
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + R_BARS);     // TMA stage landed
+    uint64_t* empty = full + R_STAGES;                               // TMA stage consumed: MMA (A) + 16 widening warps (packed B)
+    uint64_t* widened = empty + R_STAGES;                            // fp16 weight tile written
+    uint64_t* bfree = widened + R_BUFS;                              // fp16 weight tile consumed by the MMA
+    uint64_t* acc_full = bfree + R_BUFS;
+    uint64_t* acc_empty = acc_full + F_ACC;
+    uint64_t* done_bar = acc_empty + F_ACC;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
+    const int k_steps = K / 64, G = K >> 5;
+
+    if (tid == 0) {
+        for (int i = 0; i < R_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 17); }
+        for (int i = 0; i < R_BUFS; ++i) { tc::mbar_init(&widened[i], 16); tc::mbar_init(&bfree[i], 1); }
+        for (int i = 0; i < F_ACC; ++i) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 8); }
+        tc::mbar_init(done_bar, 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, 512);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(&map_p);
+            uint32_t slot = 0, phase = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
+                    uint8_t* st = smem + slot * R_STAGE;
+                    tc::mbar_expect_tx(&full[slot], RA_BYTES + QP_BYTES);
+                    tc::tma_load_2d(st, &map_a, &full[slot], ks * 64, m0);
+                    tc::tma_load_2d(st + RA_BYTES, &map_p, &full[slot], ks * 32, n0);
+                    ++issued;
+                    if (++slot == R_STAGES) { slot = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                atomicExch(err, 1);
+                for (int i = 0; i < (issued < R_STAGES ? issued : R_STAGES); ++i)
+                    for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                        if (tc::mbar_try_wait(&full[i], 0) || tc::mbar_try_wait(&full[i], 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 0, buf = 0, bphase = 0, aphase = 0;
+            const uint32_t idesc = tc::idesc_f16(FN);
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (!tc::mbar_wait(&acc_empty[0], aphase ^ 1)) { ok = false; break; }
+                tc::tc_fence_after();
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    if (!tc::mbar_wait(&full[slot], phase) || !tc::mbar_wait(&widened[buf], bphase)) { ok = false; break; }
+                    tc::tc_fence_after();
+                    const uint32_t sa = tc::smem_u32(smem + slot * R_STAGE), sb = tc::smem_u32(smem + R_BOFF + buf * QB_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {                           // rows 0-127 -> columns 0-255, rows 128-255 -> 256-511
+                        const uint64_t bdesc = smem_desc_sw128(sb + kk * 32);
+                        mma_f16(tmem, smem_desc_sw128(sa + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                        mma_f16(tmem + FN, smem_desc_sw128(sa + FM * 128 + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                    }
+                    tc::mma_commit(&empty[slot]);                              // the activation tile of this stage
+                    tc::mma_commit(&bfree[buf]);                               // and the widened weight tile are free again
+                    if (++slot == R_STAGES) { slot = 0; phase ^= 1; }
+                    if (++buf == R_BUFS) { buf = 0; bphase ^= 1; }
+                }
+                if (!ok) break;
+                tc::mma_commit(&acc_full[0]);
+                aphase ^= 1;
+            }
+            if (!ok) atomicExch(err, 2);
+            tc::mma_commit(done_bar);
+            for (uint32_t spin = 0; spin < WUSH_SPIN_LIMIT; ++spin)
+                if (tc::mbar_try_wait(done_bar, 0)) break;
+        }
+    } else if (warp >= 8 && warp < 24) {
+        // ------------------------------ widening warps -------------------------------------------
+        const int d = (tid - 256) & 255, g = (tid - 256) >> 8;     // weight row of the tile, group of the stage
+        uint32_t slot = 0, phase = 0, buf = 0, bphase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const int n = (t / tiles_m) * FN + d;
+            const bool live = n < N;
+            const float dn = live ? down[n] : 0.f;
+            // scales: one 16-byte load covers this row's 8 groups = 4 stages; the next one is in flight meanwhile
+            const uint4* srow = reinterpret_cast<const uint4*>(ws + (size_t)(live ? n : 0) * G);
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            uint4 s_cur = zero4, s_nxt = live ? __ldg(srow) : zero4;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                if ((ks & 3) == 0) {
+                    s_cur = s_nxt;
+                    if (live && ks + 4 < k_steps) s_nxt = __ldg(srow + (ks >> 2) + 1);
+                }
+                const uint32_t pair = (ks & 2) ? ((ks & 1) ? s_cur.w : s_cur.z) : ((ks & 1) ? s_cur.y : s_cur.x);   // groups 2ks, 2ks+1
+                const float s_f = g ? bf16_hi(pair) : bf16_lo(pair);
+                if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
+                const uint4 w = *reinterpret_cast<const uint4*>(smem + slot * R_STAGE + RA_BYTES + d * 32 + g * 16);
+                const __half2 s2 = __float2half2_rn(__fmul_rn(s_f, dn));                           // exact shift
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                uint4 o[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[c] = widen_word_f16(ww[c], s2);
+                __syncwarp();                                      // the packed words of this warp are in registers
+                if (lane == 0) tc::mbar_arrive(&empty[slot]);
+                if (!tc::mbar_wait(&bfree[buf], bphase ^ 1)) { ok = false; break; }
+                uint8_t* brow = smem + R_BOFF + buf * QB_BYTES + d * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(brow + (((g * 4 + c) ^ (d & 7)) << 4)) = o[c];
+                tc::fence_proxy_async();                           // generic-proxy writes -> visible to tcgen05.mma
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&widened[buf]);
+                if (++slot == R_STAGES) { slot = 0; phase ^= 1; }
+                if (++buf == R_BUFS) { buf = 0; bphase ^= 1; }
+            }
+        }
+        if (!ok && lane == 0) atomicExch(err, 8);
+    } else if (warp >= 4) {
+        const int quarter = warp & 3, upper = warp >= 24 ? 1 : 0;      // warps 4-7: rows 0-127, warps 24-27: rows 128-255
+        const int row = upper * FM + quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t ab = (uint32_t)upper;                            // column block of this half's accumulator
+        uint32_t aphase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
+            if (!tc::mbar_wait(&acc_full[0], aphase)) { ok = false; break; }
+            tc::tc_fence_after();
+            const int m = m0 + row;
+            const float fm = (m < M) ? sc.fa[m] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < FN / 32; ++c) {
+                uint32_t v[32];
+                tc::tmem_ld32(tmem + lane_base + ab * FN + c * 32, v);
+                tc::tmem_ld_wait();
+                if (c == FN / 32 - 1) {
+                    tc::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive(&acc_empty[0]);
+                }
+                const int n = n0 + c * 32;
+                if (m < M && n < N) {
+                    __half* yr = y + (size_t)m * N + n;
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        if (n + v8 * 8 + 8 <= N) {
+                            const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
+                            const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
+                            const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                            uint32_t o[4];
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
+                                                              __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
+                                o[p] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                }
+            }
+            aphase ^= 1;
+        }
+        if (!ok && lane == 0) atomicExch(err, 4);
+    }
+
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem, 512);
+}
+
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 }  // namespace
@@ -535,6 +735,7 @@ int f16_set_attributes()
     cudaError_t e = cudaFuncSetAttribute(gemm_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_fused2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_TOTAL);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "tile GEMM: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
@@ -543,8 +744,9 @@ int f16_set_attributes()
 bool f16_supported(int64_t M, int64_t N, int64_t K) { return M >= 1 && K % 64 == 0 && N % 8 == 0; }
 
 // Rows up to which the weights are widened inside the GEMM (no fp16 copy of W in the scratch).  Measured at
-// K = 8192, N = 57344: 217 vs 464 us at M = 128, 410 vs 529 us at M = 256, equal at M = 512, slower beyond.
-constexpr int64_t FUSED_MAX_ROWS = 384;
+// K = 8192, N = 57344 (us, in-kernel widening vs weight pre-pass): M = 128: 209 vs 464, 256: 277 vs 529,
+// 512: 517 vs 664, 1024: 872 vs 983, 2048: 1714 vs 1789, 4096: 3516 vs 3267.
+constexpr int64_t FUSED_MAX_ROWS = 2048;
 static bool use_fused(int64_t M, int64_t N, int64_t K) { return M <= FUSED_MAX_ROWS && K % 256 == 0; }   // whole 16-byte scale vectors
 
 // scratch: error word | fp16 activations (M x K) | [fp16 weights (N x K), unless widened in-kernel] |
@@ -571,13 +773,19 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     if (int s = check_launch("f16 pre-pass")) return s;
     CUtensorMap ma, mp;
     int s;
-    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    const bool wide = M > FM;                                          // more than one 128-row tile: 256-row tiles
+    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, wide ? 2 * FM : FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     if ((s = make_map_2d(&mp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 32, FN, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
-    const int64_t tiles = ((M + FM - 1) / FM) * ((N + FN - 1) / FN);
+    const int tile_rows = wide ? 2 * FM : FM;
+    const int64_t tiles = ((M + tile_rows - 1) / tile_rows) * ((N + FN - 1) / FN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const TileScale sc = {fa, fb, 0.f, nullptr};
-    gemm_f16_fused_kernel<<<grid, Q_THREADS, Q_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N,
-                                                            (int)K, err);
+    if (wide)
+        gemm_f16_fused2_kernel<<<grid, R_THREADS, R_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M,
+                                                                 (int)N, (int)K, err);
+    else
+        gemm_f16_fused_kernel<<<grid, Q_THREADS, Q_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N,
+                                                                (int)K, err);
     return check_launch("gemm_f16_fused");
 }
 
