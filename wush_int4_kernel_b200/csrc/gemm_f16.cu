@@ -17,13 +17,17 @@
 // Results agree with the fp64 arbiter to ~1e-6 before the fp16 output rounding; what this
 // route cannot do is expose the integer group sums (the i8 kernels do that).
 //
-// Two kernels:
-//   dequant_f16_kernel   one warp per row: codes + bf16 scales -> fp16 row (scratch) + 2^e
-//   gemm_f16_kernel      persistent 128 x 256 tiles: TMA (128-byte swizzle) -> 4-stage ring ->
-//                        tcgen05.mma kind::f16 (M=128, N=256, K=16) -> two TMEM accumulators in
-//                        rotation -> epilogue warps tcgen05.ld, scale by 2^(e_m+e_n), fp16 store
+// Kernels:
+//   dequant_f16_kernel     one warp per row: codes + bf16 scales -> fp16 row (scratch) + 2^e
+//   gemm_tile_kernel       persistent 128 x 256 tiles: TMA (128-byte swizzle) -> 4-stage ring ->
+//                          tcgen05.mma kind::f16 (M=128, N=256, K=16) -> two TMEM accumulators in
+//                          rotation -> epilogue warps tcgen05.ld, scale by 2^(e_m+e_n), fp16 store
+//                          (M > 2048: both operands pre-widened; also the kind::i8 per-tensor product)
+//   gemm_f16_fused_kernel  M <= 128: only the activations are pre-widened, the packed weight tile is
+//   gemm_f16_fused2_kernel 128 < M <= 2048 (256 x 256 tiles): widened to fp16 inside the kernel
 // Algorithmic traffic: the pre-pass reads 9/16 B and writes 2 B per operand element; the GEMM
-// reads fp16 operands (L2-resident across the M tiles that share a weight tile).
+// reads fp16 operands (L2-resident across the M tiles that share a weight tile); with in-kernel
+// widening the weights are read once, packed.
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
