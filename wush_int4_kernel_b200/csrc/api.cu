@@ -96,9 +96,11 @@ int f16_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64
 // Which kernel a shape runs on.  GEMV: CUDA cores, M <= 4 (the exact per-group scaling costs
 // three instructions per (m, n, group), so beyond a few rows the dot products must move to
 // the tensor cores).  DECODE: weights-as-wide-operand tensor-core streaming, M <= 32.
-// TILE: tcgen05 kind::i8 tile GEMM (exact integer group sums) for 32 < M < 128.
+// TILE: tcgen05 kind::i8 tile GEMM (exact integer group sums); chosen by AUTO only where the
+// streaming kernel does not take K (K % 256 != 0) at 32 < M < 128.
 // TILE_F16: scales folded into fp16 operands, tcgen05 kind::f16, for M >= 128 (several times
-// faster: no per-group epilogue; needs scratch for the fp16 operands).
+// faster: no per-group epilogue; needs scratch for the fp16 activations and, beyond 2048 rows,
+// for an fp16 copy of the weights).
 static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
 {
     if (variant != WUSH_GEMM_AUTO) return variant;
