@@ -172,7 +172,7 @@ int wush_w4a4_gemm_tensor_scale(const uint8_t* xq, const uint8_t* wq, int64_t M,
                                 void* stream);
 /* The same product with caller-provided scratch: for M >= 128 (and K % 128 == 0, N % 8 == 0)
  * both operands are widened to int8 in the scratch and contracted by tcgen05.mma kind::i8
- * tiles of 128 x 256 over the whole K (int32 accumulators in TMEM, alpha applied once).
+ * tiles of 256 x 256 over the whole K (int32 accumulators in TMEM, alpha applied once).
  * Results are bit-identical to wush_w4a4_gemm_tensor_scale.  _workspace_bytes returns 0 when
  * the shape takes the scratch-free kernel anyway; the first word of the scratch is an error
  * flag of the kernel's bounded waits (0 = fine), as for wush_w4a4_gemm. */

@@ -19,12 +19,11 @@
 //
 // Kernels:
 //   dequant_f16_kernel     one warp per row: codes + bf16 scales -> fp16 row (scratch) + 2^e
-//   gemm_f16_tile2_kernel  M > 2048, both operands pre-widened: persistent 256 x 256 tiles, TMA (128-byte
+//   gemm_tile2_kernel  M > 2048, both operands pre-widened: persistent 256 x 256 tiles, TMA (128-byte
 //                          swizzle) -> 3-stage ring -> tcgen05.mma kind::f16 (M=128, N=256, K=16), two MMA
 //                          groups per weight tile -> TMEM -> epilogue warps tcgen05.ld, scale by
 //                          2^(e_m+e_n), fp16 store
-//   gemm_tile_kernel       128 x 256 tiles, two TMEM accumulators in rotation: the kind::i8 per-tensor
-//                          product (and the fp16 form it was written for)
+//                          (instantiated for kind::i8 as well: the per-tensor-scale product)
 //   gemm_f16_fused_kernel  M <= 128: only the activations are pre-widened, the packed weight tile is
 //   gemm_f16_fused2_kernel 128 < M <= 2048 (256 x 256 tiles): widened to fp16 inside the kernel
 // Algorithmic traffic: the pre-pass reads 9/16 B and writes 2 B per operand element; the GEMM
@@ -94,12 +93,7 @@ dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restric
 // GEMM
 // ------------------------------------------------------------------------------------------------
 constexpr int FM = 128, FN = 256;                               // tile; a stage holds 128 bytes of K per row
-constexpr int F_STAGES = 4, F_ACC = 2;
-constexpr int F_THREADS = 256;                                  // warp 0 TMA, warp 1 MMA, warps 4-7 epilogue
-constexpr int FA_BYTES = FM * 128, FB_BYTES = FN * 128;
-constexpr int F_STAGE = FA_BYTES + FB_BYTES;
-constexpr int F_BARS = F_STAGES * F_STAGE;
-constexpr int F_TOTAL = F_BARS + (2 * F_STAGES + 2 * F_ACC + 1) * 8 + 16 + 1024;
+constexpr int F_ACC = 2;                                        // TMEM accumulators in rotation (128-row tiles)
 
 // K-major operand in the 128-byte-swizzled layout TMA writes: rows of 128 B, 8-row groups 1 KB apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
@@ -129,164 +123,6 @@ struct TileScale {
     float alpha;
     const float* alpha_dev;
 };
-
-// I8 = false: fp16 operands, 64 elements per 128-byte stage row, tcgen05.mma kind::f16 (K = 16);
-// I8 = true:  int8 operands, 128 elements per stage row, kind::i8 (K = 32), int32 accumulators.
-// Either way a stage row is 128 bytes and one MMA advances 32 bytes along it.
-template <bool I8>
-__global__ void __launch_bounds__(F_THREADS, 1)
-gemm_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const TileScale sc, __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
-{
-    constexpr int FK = I8 ? 128 : 64;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + F_BARS);
-    uint64_t* empty = full + F_STAGES;
-    uint64_t* acc_full = empty + F_STAGES;
-    uint64_t* acc_empty = acc_full + F_ACC;
-    uint64_t* done_bar = acc_empty + F_ACC;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tiles_m = (M + FM - 1) / FM, tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
-    const int k_steps = K / FK;
-
-    if (tid == 0) {
-        for (int i = 0; i < F_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
-        for (int i = 0; i < F_ACC; ++i) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 4); }
-        tc::mbar_init(done_bar, 1);
-        tc::mbar_fence_init();
-    }
-    if (warp == 1) {
-        tc::tmem_alloc(tmem_slot, 512);
-        tc::tmem_relinquish();
-    }
-    tc::tc_fence_before();
-    __syncthreads();
-    tc::tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(&map_b);
-            uint32_t slot = 0, phase = 0;
-            int issued = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
-                for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
-                    uint8_t* st = smem + slot * F_STAGE;
-                    tc::mbar_expect_tx(&full[slot], F_STAGE);
-                    tc::tma_load_2d(st, &map_a, &full[slot], ks * FK, m0);
-                    tc::tma_load_2d(st + FA_BYTES, &map_b, &full[slot], ks * FK, n0);
-                    ++issued;
-                    if (++slot == F_STAGES) { slot = 0; phase ^= 1; }
-                }
-            }
-            if (!ok) {
-                atomicExch(err, 1);
-                for (int i = 0; i < (issued < F_STAGES ? issued : F_STAGES); ++i)
-                    for (uint32_t spin = 0; spin < (1u << 16); ++spin)
-                        if (tc::mbar_try_wait(&full[i], 0) || tc::mbar_try_wait(&full[i], 1)) break;
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            uint32_t slot = 0, phase = 0, ab = 0, aphase = 0;
-            const uint32_t idesc = I8 ? tc::idesc_i8(FN) : tc::idesc_f16(FN);
-            bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                if (!tc::mbar_wait(&acc_empty[ab], aphase ^ 1)) { ok = false; break; }
-                tc::tc_fence_after();
-                for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
-                    tc::tc_fence_after();
-                    const uint32_t sa = tc::smem_u32(smem + slot * F_STAGE), sb = sa + FA_BYTES;
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {                           // 32 bytes further along K inside the swizzled row
-                        if constexpr (I8)
-                            tc::mma_i8(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
-                                       (ks | kk) ? 1u : 0u);
-                        else
-                            mma_f16(tmem + ab * FN, smem_desc_sw128(sa + kk * 32), smem_desc_sw128(sb + kk * 32), idesc,
-                                    (ks | kk) ? 1u : 0u);
-                    }
-                    tc::mma_commit(&empty[slot]);                              // stage free once these MMAs retire
-                    if (++slot == F_STAGES) { slot = 0; phase ^= 1; }
-                }
-                if (!ok) break;
-                tc::mma_commit(&acc_full[ab]);
-                if (++ab == F_ACC) { ab = 0; aphase ^= 1; }
-            }
-            if (!ok) atomicExch(err, 2);
-            tc::mma_commit(done_bar);
-            for (uint32_t spin = 0; spin < WUSH_SPIN_LIMIT; ++spin)
-                if (tc::mbar_try_wait(done_bar, 0)) break;
-        }
-    } else if (warp >= 4) {
-        const int quarter = warp & 3, row = quarter * 32 + lane;
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        uint32_t ab = 0, aphase = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
-            if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
-            tc::tc_fence_after();
-            const int m = m0 + row;
-            float fm;
-            if constexpr (I8) fm = sc.alpha_dev ? __ldg(sc.alpha_dev) : sc.alpha;
-            else fm = (m < M) ? sc.fa[m] : 0.f;
-#pragma unroll 1
-            for (int c = 0; c < FN / 32; ++c) {
-                uint32_t v[32];
-                tc::tmem_ld32(tmem + lane_base + ab * FN + c * 32, v);
-                tc::tmem_ld_wait();
-                if (c == FN / 32 - 1) {                        // accumulator fully read: hand it back
-                    tc::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) tc::mbar_arrive(&acc_empty[ab]);
-                }
-                const int n = n0 + c * 32;
-                if (m < M && n < N) {
-                    __half* yr = y + (size_t)m * N + n;
-#pragma unroll
-                    for (int v8 = 0; v8 < 4; ++v8) {
-                        if (n + v8 * 8 + 8 <= N) {
-                            uint32_t o[4];
-                            if constexpr (I8) {
-#pragma unroll
-                                for (int p = 0; p < 4; ++p) {                  // |acc| < 2^24: the conversion is exact
-                                    __half2 h = __floats2half2_rn(__fmul_rn(fm, (float)(int)v[v8 * 8 + 2 * p]),
-                                                                  __fmul_rn(fm, (float)(int)v[v8 * 8 + 2 * p + 1]));
-                                    o[p] = *reinterpret_cast<uint32_t*>(&h);
-                                }
-                            } else {
-                                const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
-                                const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
-                                const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-#pragma unroll
-                                for (int p = 0; p < 4; ++p) {
-                                    __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
-                                                                  __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
-                                    o[p] = *reinterpret_cast<uint32_t*>(&h);
-                                }
-                            }
-                            *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
-                    }
-                }
-            }
-            if (++ab == F_ACC) { ab = 0; aphase ^= 1; }
-        }
-        if (!ok && lane == 0) atomicExch(err, 4);
-    }
-
-    tc::tc_fence_before();
-    __syncthreads();
-    if (warp == 1) tc::tmem_dealloc(tmem, 512);
-}
 
 // ------------------------------------------------------------------------------------------------
 // The same product with the weights widened INSIDE the kernel (M up to a few thousand rows)
@@ -734,7 +570,8 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 // ------------------------------------------------------------------------------------------------
 // Pre-widened operands on 256 x 256 tiles (M > 2048)
 // ------------------------------------------------------------------------------------------------
-// Same data flow as gemm_tile_kernel<false>, but one fp16 weight tile per stage feeds two MMA groups
+// TMA (128-byte swizzle) -> ring of stages -> tcgen05.mma -> TMEM -> epilogue warps; one weight tile per
+// stage feeds two MMA groups
 // (activation rows 0-127 -> TMEM columns 0-255, rows 128-255 -> columns 256-511): 64 KB of TMA writes
 // and 96 KB of operand reads per 1240 MMA cycles instead of 48 + 48 KB per 620, which is what the
 // shared memory of a multiprocessor can sustain.  The accumulator pair fills the TMEM, so the epilogue
@@ -746,8 +583,9 @@ constexpr int T_STAGE = TA_BYTES + TB_BYTES;                     // 64 KB
 constexpr int T_BARS = T_STAGES * T_STAGE;
 constexpr int T_TOTAL = T_BARS + (2 * T_STAGES + 2 + 1) * 8 + 16 + 1024;
 
+template <bool I8>
 __global__ void __launch_bounds__(T_THREADS, 1)
-gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TileScale sc,
+gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TileScale sc,
                       __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -761,7 +599,7 @@ gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
-    const int k_steps = K / 64;
+    const int k_steps = K / (I8 ? 128 : 64);                 // a stage row is 128 bytes either way
 
     if (tid == 0) {
         for (int i = 0; i < T_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
@@ -791,8 +629,8 @@ gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
                     uint8_t* st = smem + slot * T_STAGE;
                     tc::mbar_expect_tx(&full[slot], T_STAGE);
-                    tc::tma_load_2d(st, &map_a, &full[slot], ks * 64, m0);
-                    tc::tma_load_2d(st + TA_BYTES, &map_b, &full[slot], ks * 64, n0);
+                    tc::tma_load_2d(st, &map_a, &full[slot], ks * (I8 ? 128 : 64), m0);
+                    tc::tma_load_2d(st + TA_BYTES, &map_b, &full[slot], ks * (I8 ? 128 : 64), n0);
                     ++issued;
                     if (++slot == T_STAGES) { slot = 0; phase ^= 1; }
                 }
@@ -807,7 +645,7 @@ gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     } else if (warp == 1) {
         if (lane == 0) {
             uint32_t slot = 0, phase = 0, aphase = 0;
-            const uint32_t idesc = tc::idesc_f16(FN);
+            const uint32_t idesc = I8 ? tc::idesc_i8(FN) : tc::idesc_f16(FN);
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 if (!tc::mbar_wait(acc_empty, aphase ^ 1)) { ok = false; break; }
@@ -819,8 +657,13 @@ gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
                         const uint64_t bdesc = smem_desc_sw128(sb + kk * 32);
-                        mma_f16(tmem, smem_desc_sw128(sa + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
-                        mma_f16(tmem + FN, smem_desc_sw128(sa + FM * 128 + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                        if constexpr (I8) {
+                            tc::mma_i8(tmem, smem_desc_sw128(sa + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                            tc::mma_i8(tmem + FN, smem_desc_sw128(sa + FM * 128 + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                        } else {
+                            mma_f16(tmem, smem_desc_sw128(sa + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                            mma_f16(tmem + FN, smem_desc_sw128(sa + FM * 128 + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                        }
                     }
                     tc::mma_commit(&empty[slot]);
                     if (++slot == T_STAGES) { slot = 0; phase ^= 1; }
@@ -845,7 +688,9 @@ gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             if (!tc::mbar_wait(acc_full, aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
-            const float fm = (m < M) ? sc.fa[m] : 0.f;
+            float fm;
+            if constexpr (I8) fm = sc.alpha_dev ? __ldg(sc.alpha_dev) : sc.alpha;
+            else fm = (m < M) ? sc.fa[m] : 0.f;
 #pragma unroll 1
             for (int c = 0; c < FN / 32; ++c) {
                 uint32_t v[32];
@@ -862,15 +707,24 @@ gemm_f16_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                     for (int v8 = 0; v8 < 4; ++v8) {
                         if (n + v8 * 8 + 8 <= N) {
-                            const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
-                            const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
-                            const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
                             uint32_t o[4];
+                            if constexpr (I8) {
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) {
-                                __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
-                                                              __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
-                                o[p] = *reinterpret_cast<uint32_t*>(&h);
+                                for (int p = 0; p < 4; ++p) {                  // |acc| < 2^24: the conversion is exact
+                                    __half2 h = __floats2half2_rn(__fmul_rn(fm, (float)(int)v[v8 * 8 + 2 * p]),
+                                                                  __fmul_rn(fm, (float)(int)v[v8 * 8 + 2 * p + 1]));
+                                    o[p] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                            } else {
+                                const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
+                                const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
+                                const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+                                for (int p = 0; p < 4; ++p) {
+                                    __half2 h = __floats2half2_rn(__uint_as_float(v[v8 * 8 + 2 * p]) * (fm * fs[2 * p]),
+                                                                  __uint_as_float(v[v8 * 8 + 2 * p + 1]) * (fm * fs[2 * p + 1]));
+                                    o[p] = *reinterpret_cast<uint32_t*>(&h);
+                                }
                             }
                             *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
                         }
@@ -894,10 +748,10 @@ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 int f16_set_attributes()
 {
     if (int s = resolve_tensor_map_encoder()) return s;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(gemm_f16_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_TOTAL);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_fused2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_tile2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tile2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tile2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_TOTAL);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "tile GEMM: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
@@ -979,7 +833,7 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     const int64_t tiles = ((M + 2 * FM - 1) / (2 * FM)) * ((N + FN - 1) / FN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const TileScale sc = {fa, fb, 0.f, nullptr};
-    gemm_f16_tile2_kernel<<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
+    gemm_tile2_kernel<false><<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
     return check_launch("gemm_f16");
 }
 
@@ -1042,12 +896,12 @@ int i8_tile_dispatch(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N,
     if (int s = check_launch("widen_s8")) return s;
     CUtensorMap ma, mb;
     int s;
-    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a8, K, M, 128, FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
+    if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a8, K, M, 128, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b8, K, N, 128, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
-    const int64_t tiles = ((M + FM - 1) / FM) * ((N + FN - 1) / FN);
+    const int64_t tiles = ((M + 2 * FM - 1) / (2 * FM)) * ((N + FN - 1) / FN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const TileScale sc = {nullptr, nullptr, alpha, alpha_dev};
-    gemm_tile_kernel<true><<<grid, F_THREADS, F_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
+    gemm_tile2_kernel<true><<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
     return check_launch("gemm_i8_tile");
 }
 
