@@ -1,7 +1,7 @@
 """Measurement matrix over the layer shapes the reference quotes (``bench/exp_p13_official.py:42-63``
 draws random tensors of the same shapes; no dataset or checkpoint is involved).
 
-    python -m wush_int4_kernel_b200.bench_matrix [--configs qwen,llama,square,prefill,ffn] [--tp P]
+    python -m wush_int4_kernel_b200.bench_matrix [--configs qwen,llama,mid,square,prefill,ffn] [--tp P]
     torchrun --nproc-per-node P -m wush_int4_kernel_b200.bench_matrix --configs ffn
 
 For every (K, N, M) one JSON line with the time of the fused transform+quantisation, of the
@@ -32,6 +32,7 @@ INT8_MEASURED_TOPS = 3800.0        # MMA-only tcgen05 kind::i8 probe, 128 x 256 
 SHAPES = {                      # name -> (K, N, rows per step)
     "qwen": (4096, 24576, (1, 8, 32)),
     "llama": (8192, 57344, (1, 2, 4, 8, 16, 32)),
+    "mid": (8192, 57344, (64, 128, 256)),
     "square": (4096, 4096, (4096,)),
     "prefill": (8192, 57344, (512, 2048, 4096)),
 }
