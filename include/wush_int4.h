@@ -97,14 +97,16 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  * Replaces w4a4_gemm_s4 (csrc/gemm_s4.cu:320-379), w4a4_gemm / _v1 / _v2
  * (csrc/gemm_int4.cu:89-130, csrc/gemm_wmma.cu:128-172, csrc/gemm_wmma2.cu:141-181),
  * w4a4_gemv and w4a4_gemv_multi (csrc/gemv_int4.cu:145-223).
- *   WUSH_GEMM_AUTO     : pick by M (GEMV for M <= 2, DECODE up to 32, TILE up to 127,
- *                        TILE_F16 from 128)
+ *   WUSH_GEMM_AUTO     : pick by shape (GEMV for M <= 2, and for M <= 4 on narrow layers;
+ *                        DECODE up to 127 rows; TILE_F16 from 128; TILE only where DECODE
+ *                        does not take K)
  *   WUSH_GEMM_GEMV     : CUDA-core streaming kernel (M <= 4)
  *   WUSH_GEMM_DECODE   : tensor-core streaming kernel, weights as the wide operand (any M)
  *   WUSH_GEMM_TILE     : tcgen05 kind::i8 tile GEMM, exact int32 sum per group (any M)
  *   WUSH_GEMM_TILE_F16 : scales folded into exactly-representable fp16 operands, tcgen05
  *                        kind::f16 with fp32 accumulation over the whole K (any M; the fast
- *                        route for prefill; scratch = fp16 copies of both operands)
+ *                        route for prefill; scratch = an fp16 copy of the activations and,
+ *                        beyond 2048 rows, of the weights)
  * K % 32 == 0.  Ask wush_w4a4_gemm_workspace_bytes() with the SAME variant for the scratch
  * size; `workspace` may be NULL when it returns 0.  Word 0 of the scratch is an error word:
  * non-zero after the call completes means a bounded wait inside the kernel gave up. */
@@ -128,7 +130,7 @@ int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const v
  * wush_w4a4_gemm(..., WUSH_GEMM_TILE_F16, ...), but the scratch is an array of
  * WUSH_STATIC_SCRATCH_BYTES that is part of the library image: every GPU that loads the library
  * keeps it until the process exits, so the limit is deliberately modest.
- *   - Shapes whose scratch (about 2*(M+N)*K bytes) exceeds the limit are refused with
+ *   - Shapes whose scratch (about 2*M*K bytes up to 2048 rows, 2*(M+N)*K beyond) exceeds the limit are refused with
  *     WUSH_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
  *   - Neither this call nor anything it uses calls cudaMalloc / cudaFree or an allocating
  *     library routine.
