@@ -98,8 +98,9 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  * (csrc/gemm_int4.cu:89-130, csrc/gemm_wmma.cu:128-172, csrc/gemm_wmma2.cu:141-181),
  * w4a4_gemv and w4a4_gemv_multi (csrc/gemv_int4.cu:145-223).
  *   WUSH_GEMM_AUTO     : pick by shape (GEMV for M <= 2, and for M <= 4 on narrow layers;
- *                        DECODE up to 127 rows; TILE_F16 from 128; TILE only where DECODE
- *                        does not take K)
+ *                        DECODE up to 32 rows; for 32 < M <= 512 the cheaper of DECODE in
+ *                        32-row blocks and TILE_F16 by a measured cost estimate in N, K and
+ *                        M; TILE_F16 beyond; TILE only where neither takes K)
  *   WUSH_GEMM_GEMV     : CUDA-core streaming kernel (M <= 4)
  *   WUSH_GEMM_DECODE   : tensor-core streaming kernel, weights as the wide operand (any M)
  *   WUSH_GEMM_TILE     : tcgen05 kind::i8 tile GEMM, exact int32 sum per group (any M)

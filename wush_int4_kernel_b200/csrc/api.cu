@@ -109,10 +109,28 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
     // ones (a CTA of the streaming kernel is left with one or two warps there)
     if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0 || N <= 16384)) return WUSH_GEMM_GEMV;
     if (M <= 32) return WUSH_GEMM_DECODE;
-    if (M >= 128 && f16_supported(M, N, K)) return WUSH_GEMM_TILE_F16;
-    // 32 < M < 128: the streaming kernel in blocks of 32 rows (measured 2 x faster at M = 64 than a
-    // half-empty 128-row tile); the exact tile kernel where the streaming kernel does not take K
-    if (K % 256 == 0) return WUSH_GEMM_DECODE;
+    const bool f16_ok = f16_supported(M, N, K), stream_ok = K % 256 == 0;
+    if (f16_ok && stream_ok && M <= 512) {
+        // Both routes take the shape: the streaming kernel runs once per block of 32 rows and scales with
+        // the layer, the fp16 route has a floor of one tile per multiprocessor over the whole K.  Times in
+        // microseconds from measurements on the 70B gate+up layer (4.7e8 weights) and on narrow layers.
+        const double elems = (double)N * (double)K, unit = elems / 4.7e8;
+        const double chain = (double)K / 128.0 * 0.38;                    // a CTA's serial walk over K
+        const int64_t full_blocks = M / 32, rest = M % 32;
+        double t_stream = (double)full_blocks * (121.0 * unit > chain ? 121.0 * unit : chain);
+        if (rest) {
+            const double t = (rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : 121.0) * unit;
+            t_stream += t > chain ? t : chain;
+        }
+        const int64_t tiles = (M <= 128 ? 1 : (M + 255) / 256) * ((N + 255) / 256);
+        const double waves = (double)((tiles + sm_count() - 1) / sm_count());
+        const double t_f16 = waves * (double)K / 64.0 * (M <= 128 ? 0.8 : 1.05) + 30.0;
+        return t_stream <= t_f16 ? WUSH_GEMM_DECODE : WUSH_GEMM_TILE_F16;
+    }
+    if (M >= 128 && f16_ok) return WUSH_GEMM_TILE_F16;
+    // 32 < M < 128 otherwise: the streaming kernel in blocks of 32 rows; the exact tile kernel where the
+    // streaming kernel does not take K
+    if (stream_ok) return WUSH_GEMM_DECODE;
     return tc_supported(M, N, K) ? WUSH_GEMM_TILE : WUSH_GEMM_DECODE;
 }
 
