@@ -196,8 +196,8 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
  *                      2n <= slot_bytes; every rank must call it the same number of times with the
  *                      same n.  One kernel launch, no host synchronisation, capturable; a rank waits for
  *                      its peers inside the kernel for about a second at most, then records an error;
- *   wush_comm_gemv_allreduce   decode product (M <= 2, the operands of wush_w4a4_gemm) AND the sum over
- *                      ranks: the product kernel's epilogue stores its fp16 result into every rank's
+ *   wush_comm_gemv_allreduce   decode product (the operands of wush_w4a4_gemm; M <= 2 by the CUDA-core
+ *                      GEMV, M <= 32 with K % 256 == 0 by the streaming kernel) AND the sum over ranks: the product kernel's epilogue stores its fp16 result into every rank's
  *                      buffer over NVLink and its last CTA publishes the step; the reduction then reads
  *                      local memory only.  WUSH_ERR_UNSUPPORTED for other shapes (use wush_w4a4_gemm +
  *                      wush_comm_allreduce_f16).  Same calling discipline as wush_comm_allreduce_f16, and

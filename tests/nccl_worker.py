@@ -59,7 +59,7 @@ def main():
     assert peer.error() == 0
     # fused product + exchange (decode rows): equals product followed by the pull all-reduce, bit for bit
     from wush_int4_kernel_b200.linear import quantise_activations, w4a4_product
-    for rows in (1, 2, 1):
+    for rows in (1, 2, 1, 8, 32, 5):
         xr = synth.draw_activations(rows, 1024, layer.outliers, gen)[:, k0:k1].contiguous()
         shard = RowParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, reduce_output=False)
         xq_l, xs_l = quantise_activations(xr, shard.local.t)

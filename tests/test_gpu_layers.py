@@ -180,7 +180,8 @@ def test_peer_allreduce_wait_runs_out():
         capi.check(lib.wush_comm_destroy(other), "comm_destroy")
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 768, 1024), (2, 1000, 4096), (1, 8192, 3584), (2, 264, 256)])
+@pytest.mark.parametrize("M,N,K", [(1, 768, 1024), (2, 1000, 4096), (1, 8192, 3584), (2, 264, 256),
+                                   (3, 768, 1024), (8, 1000, 4096), (13, 264, 256), (24, 776, 512), (32, 768, 2048)])
 def test_pushed_gemv_allreduce_single_rank(setup, M, N, K):
     """World of one: the product kernel writes into the exchange buffer instead of y, publishes,
     and the reduction returns it -- byte-identical to the plain product, several steps in a row
@@ -194,7 +195,7 @@ def test_pushed_gemv_allreduce_single_rank(setup, M, N, K):
     wq = torch.randint(0, 256, (N, K // 2), generator=gen, device="cuda", dtype=torch.uint8)
     xs = (0.02 * (1 + torch.rand(M, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
     ws = (0.01 * (1 + torch.rand(N, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
-    expect = cabi.gemm(xq, xs, wq, ws)
+    expect = cabi.gemm(xq, xs, wq, ws, capi.GEMM_GEMV if M <= 2 else capi.GEMM_DECODE)   # the kernel that pushes
     comm = ctypes.c_void_p()
     capi.check(lib.wush_comm_create(0, 1, 64 * 1024, ctypes.byref(comm)), "comm_create")
     try:
@@ -207,9 +208,9 @@ def test_pushed_gemv_allreduce_single_rank(setup, M, N, K):
             plain = torch.zeros_like(expect)
             capi.check(lib.wush_comm_allreduce_f16(comm, expect.data_ptr(), plain.data_ptr(), expect.numel(), stream), "allreduce")
             assert torch.equal(plain, expect)
-        x3 = torch.zeros(3, K // 2, dtype=torch.uint8, device="cuda")
-        assert lib.wush_comm_gemv_allreduce(comm, x3.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(), 3, N, K,
-                                            out.data_ptr(), stream) == 3          # WUSH_ERR_UNSUPPORTED: more than two rows
+        x33 = torch.zeros(33, K // 2, dtype=torch.uint8, device="cuda")
+        assert lib.wush_comm_gemv_allreduce(comm, x33.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(), 33, N, K,
+                                            out.data_ptr(), stream) == 3          # WUSH_ERR_UNSUPPORTED: more than 32 rows
         err = ctypes.c_int(-1)
         capi.check(lib.wush_comm_error(comm, ctypes.byref(err)), "comm_error")
         assert err.value == 0

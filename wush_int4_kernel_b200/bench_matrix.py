@@ -146,7 +146,8 @@ def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None) -
     elif peer is None or M * hidden > peer.max_elements:
         reduce_kind = "nccl fp32"
     else:
-        reduce_kind = "peer memory, pushed from the product kernel" if M <= 2 else "peer memory, one kernel"
+        pushed = M <= 2 or (M <= 32 and (il) % 256 == 0)
+        reduce_kind = "peer memory, pushed from the product kernel" if pushed else "peer memory, one kernel"
     return {"block": "ffn 8192 -> 2 x 28672 -> 8192", "M": M, "tp": tp, "all_reduce": reduce_kind, "graph": captured,
             "us_per_block": round(t, 2), "eff_tops_whole_block": round(ops_total / t / 1e6, 2),
             "weight_bytes_per_rank": wbytes, "weight_stream_gbs_per_rank": round(wbytes / t / 1e3, 1)}

@@ -32,6 +32,7 @@
 //
 // Algorithmic HBM bytes: 9*N*K/16 (weights) + 9*M*K/16 (activations, L2 resident) + 2*M*N.
 #include "common.cuh"
+#include "peer_common.cuh"
 #include "tc_common.cuh"
 #include "tc_host.cuh"
 
@@ -101,12 +102,17 @@ __device__ __forceinline__ float scale_of(const uint2& v, int e) {
 }
 
 // `warps` compute warps own 16 weight rows each; warp index `warps` is the TMA producer.
-template <int MT, bool PARTIALS>
+// PUSH (one block of rows, gridDim.y == 1): instead of y the result goes into slot (step & 1, rank)
+// of EVERY rank's exchange buffer, stored over NVLink from the epilogue; the CTA's last compute warp
+// counts the CTA and the grid's last CTA publishes the step (peer_common.cuh).
+template <int MT, bool PARTIALS, bool PUSH = false>
 __global__ void __launch_bounds__((max_warps(MT) + ST_EXTRA_WARPS) * 32, 2)
 w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_constant__ CUtensorMap map_xq,
                    const __grid_constant__ CUtensorMap map_ws, const __grid_constant__ CUtensorMap map_xs,
-                   __half* __restrict__ y, int32_t* __restrict__ part, int M, int N, int K, int warps)
+                   __half* __restrict__ y, int32_t* __restrict__ part, int M, int N, int K, int warps,
+                   const PeerTable peers)
 {
+    __shared__ unsigned int s_warps_done;
     constexpr int XROWS = MT * 8;
     const StreamPlan L(warps, XROWS);
     extern __shared__ uint8_t smem_raw[];
@@ -122,6 +128,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < L.stages; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], warps); tc::mbar_init(&xready[i], 1); }
         tc::mbar_fence_init();
+        s_warps_done = 0;
     }
     __syncthreads();
 
@@ -294,9 +301,34 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
     }
     if (!ok) {
         if (lane == 0) atomicExch(&g_device_flag, 2);
-        return;
+        if constexpr (!PUSH) return;                          // PUSH: still count the CTA, the peers wait for the flag
     }
-    if constexpr (!PARTIALS) {
+    if constexpr (PUSH) {
+        const int na = n_base + warp * 16 + gid, nb = na + 8;
+        const float k = 1.0f / 256.0f;
+        // the step counter is stable: the reduction of the previous step has completed on this stream
+        const unsigned int step = *reinterpret_cast<volatile unsigned int*>(&peers.state->step);
+        const size_t off = slot_offset(peers, step, peers.rank);
+        if (ok) {
+            for (int p = 0; p < peers.world; ++p) {
+                __half* dst = reinterpret_cast<__half*>(peers.base[p] + off);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int m0 = m_base + mt * 8 + tig * 2, m1 = m0 + 1;
+                    if (m0 < M && na < N) dst[(size_t)m0 * N + na] = __float2half_rn(acc[mt][0].x * k);
+                    if (m1 < M && na < N) dst[(size_t)m1 * N + na] = __float2half_rn(acc[mt][0].y * k);
+                    if (m0 < M && nb < N) dst[(size_t)m0 * N + nb] = __float2half_rn(acc[mt][1].x * k);
+                    if (m1 < M && nb < N) dst[(size_t)m1 * N + nb] = __float2half_rn(acc[mt][1].y * k);
+                }
+            }
+        }
+        __threadfence_system();
+        __syncwarp();
+        unsigned int finished = 0;
+        if (lane == 0) finished = atomicAdd(&s_warps_done, 1u);
+        finished = __shfl_sync(0xffffffffu, finished, 0);
+        if (finished == (unsigned int)warps - 1) comm_count_and_publish(peers, step, lane);
+    } else if constexpr (!PARTIALS) {
         const int na = n_base + warp * 16 + gid, nb = na + 8;
         const float k = 1.0f / 256.0f;
 #pragma unroll
@@ -324,9 +356,9 @@ int pick_warps(int64_t N, int64_t m_blocks, int limit)
     return (int)w;
 }
 
-template <int MT, bool PARTIALS>
+template <int MT, bool PARTIALS, bool PUSH = false>
 int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
-                  void* y, int32_t* part, cudaStream_t st)
+                  void* y, int32_t* part, cudaStream_t st, const PeerTable& peers = PeerTable{})
 {
     constexpr int XROWS = MT * 8;
     const int64_t m_blocks = (M + XROWS - 1) / XROWS;
@@ -340,14 +372,15 @@ int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const vo
     if ((s = make_map_2d(&mws, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ws, K / 32, N, ST_SG, L.rows, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
     if ((s = make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, K / 32, M, ST_SG, XROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
     dim3 grid((unsigned)((N + L.rows - 1) / L.rows), (unsigned)m_blocks);
-    w4a4_stream_kernel<MT, PARTIALS><<<grid, (warps + ST_EXTRA_WARPS) * 32, L.total, st>>>(mwq, mxq, mws, mxs, (__half*)y, part, (int)M,
-                                                                              (int)N, (int)K, warps);
+    if (PUSH && grid.y != 1) return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode, pushed): one block of rows only");
+    w4a4_stream_kernel<MT, PARTIALS, PUSH><<<grid, (warps + ST_EXTRA_WARPS) * 32, L.total, st>>>(
+        mwq, mxq, mws, mxs, (__half*)y, part, (int)M, (int)N, (int)K, warps, peers);
     return check_launch("w4a4_stream");
 }
 
-template <int MT, bool P>
+template <int MT, bool P, bool PUSH = false>
 cudaError_t set_attr() {
-    return cudaFuncSetAttribute(w4a4_stream_kernel<MT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    return cudaFuncSetAttribute(w4a4_stream_kernel<MT, P, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
 }
 
 }  // namespace
@@ -357,7 +390,9 @@ int stream_set_attributes()
     if (int s = resolve_tensor_map_encoder()) return s;
     cudaError_t e;
     if ((e = set_attr<1, false>()) != cudaSuccess || (e = set_attr<2, false>()) != cudaSuccess ||
-        (e = set_attr<4, false>()) != cudaSuccess || (e = set_attr<4, true>()) != cudaSuccess)
+        (e = set_attr<4, false>()) != cudaSuccess || (e = set_attr<4, true>()) != cudaSuccess ||
+        (e = set_attr<1, false, true>()) != cudaSuccess || (e = set_attr<2, false, true>()) != cudaSuccess ||
+        (e = set_attr<4, false, true>()) != cudaSuccess)
         return fail(WUSH_ERR_CUDA, "decode kernel: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
@@ -374,6 +409,16 @@ int stream_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const 
     if (M <= 8) return launch_stream<1, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
     if (M <= 16) return launch_stream<2, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
     return launch_stream<4, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
+}
+
+// M <= 32: the result goes into every rank's exchange slot instead of y (see the kernel).
+int stream_dispatch_push(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
+                         const PeerTable& peers, cudaStream_t st)
+{
+    if (M <= 8) return launch_stream<1, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
+    if (M <= 16) return launch_stream<2, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
+    if (M <= 32) return launch_stream<4, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
+    return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode, pushed): at most 32 rows");
 }
 
 int stream_partials(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N, int64_t K, int32_t* P, cudaStream_t st)

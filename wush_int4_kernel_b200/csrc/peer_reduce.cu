@@ -281,14 +281,19 @@ WUSH_API int wush_comm_allreduce_f16(void* comm, const void* partial, void* out,
     return launch_reduce(c, t, partial, out, n, 0, (cudaStream_t)stream);
 }
 
-// Product of the decode GEMV and the sum over ranks as one chain of two kernels that share the
-// exchange: the GEMV's epilogue stores into every rank's slot, its last CTA publishes, the
-// reduction reads only local memory.  WUSH_ERR_UNSUPPORTED for shapes the GEMV does not take
-// (M > 2, huge K) or results that do not fit a slot: use wush_w4a4_gemm + wush_comm_allreduce_f16.
+// Decode product and the sum over ranks as one chain of two kernels that share the exchange: the
+// product's epilogue stores into every rank's slot, its last CTA publishes, the reduction reads
+// only local memory.  M <= 2 runs the CUDA-core GEMV, 3 <= M <= 32 (and M <= 2 with a K the GEMV
+// does not hold in shared memory) the tensor-core streaming kernel (K % 256 == 0).
+// WUSH_ERR_UNSUPPORTED for other shapes or results that do not fit a slot: use wush_w4a4_gemm +
+// wush_comm_allreduce_f16.
 namespace wush {
 int gemv_dispatch_push(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, const PeerTable&,
                        cudaStream_t);
 size_t gemv_smem_bytes(int M, int64_t K);
+int stream_dispatch_push(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, const PeerTable&,
+                         cudaStream_t);
+bool stream_supported(int64_t K, const void* xs, const void* ws);
 }
 
 WUSH_API int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws,
@@ -300,12 +305,16 @@ WUSH_API int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void*
     WUSH_REQUIRE(M >= 1 && N >= 1 && K > 0 && K % 32 == 0, "comm_gemv_allreduce: bad shape");
     WUSH_REQUIRE(xq && xs && wq && ws && out, "comm_gemv_allreduce: null pointer");
     WUSH_REQUIRE(aligned16(xq) && aligned16(wq) && aligned16(out), "comm_gemv_allreduce: pointers must be 16-byte aligned");
-    if (M > 2 || (M * N) % 8 != 0 || (size_t)(M * N) * 2 > c->slot_bytes || gemv_smem_bytes((int)M, K) > 200 * 1024)
-        return fail(WUSH_ERR_UNSUPPORTED, "comm_gemv_allreduce: M=%lld N=%lld K=%lld is outside the pushed GEMV's range",
+    const bool by_gemv = M <= 2 && gemv_smem_bytes((int)M, K) <= 200 * 1024;
+    const bool by_stream = M <= 32 && stream_supported(K, xs, ws);
+    if ((!by_gemv && !by_stream) || (M * N) % 8 != 0 || (size_t)(M * N) * 2 > c->slot_bytes)
+        return fail(WUSH_ERR_UNSUPPORTED, "comm_gemv_allreduce: M=%lld N=%lld K=%lld is outside the pushed kernels' range",
                     (long long)M, (long long)N, (long long)K);
     PeerTable t;
     if (int s = fill_table(c, &t, "comm_gemv_allreduce")) return s;
-    if (int s = gemv_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream)) return s;
+    if (int s = by_gemv ? gemv_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream)
+                        : stream_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream))
+        return s;
     return launch_reduce(c, t, nullptr, out, M * N, 1, (cudaStream_t)stream);
 }
 

@@ -133,7 +133,7 @@ class RowParallelW4A4Linear:
         return self.product_and_reduce(xq, xs).reshape(*lead, self.local.out_features)
 
     def product_and_reduce(self, xq: torch.Tensor, xs: torch.Tensor) -> torch.Tensor:
-        """Local product of already quantised activations, then the sum over ranks; at most two
+        """Local product of already quantised activations, then the sum over ranks; at most 32
         rows with a peer communicator attached run as the fused product + exchange chain."""
         peer = getattr(self, "peer_reduce", None)
         if peer is not None and self.reduce_output and self.world > 1:

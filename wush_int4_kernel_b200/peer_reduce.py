@@ -51,12 +51,16 @@ class PeerAllReduce:
         return out
 
     def product_allreduce(self, xq, xs, wq, ws):
-        """Decode product (at most two activation rows) and the sum over ranks in one chain: the
-        product kernel pushes its result into every rank's buffer.  Returns ``None`` for shapes
-        outside that kernel's range (the caller then uses the product op followed by ``__call__``)."""
+        """Decode product (at most 32 activation rows) and the sum over ranks in one chain: the
+        product kernel pushes its result into every rank's buffer (the CUDA-core GEMV up to two
+        rows, the tensor-core streaming kernel up to 32 where K % 256 == 0).  Returns ``None`` for
+        shapes outside those kernels' range (the caller then uses the product op followed by
+        ``__call__``)."""
         K = wq.shape[1] * 2
         rows, n = xq.numel() // (K // 2), wq.shape[0]
-        if rows > 2 or (rows * n) % 8 or rows * n > self.max_elements or rows * (K // 32) * 36 > 200 * 1024:
+        by_gemv = rows <= 2 and rows * (K // 32) * 36 <= 200 * 1024
+        by_stream = rows <= 32 and K % 256 == 0 and xs.data_ptr() % 16 == 0 and ws.data_ptr() % 16 == 0
+        if not (by_gemv or by_stream) or (rows * n) % 8 or rows * n > self.max_elements:
             return None
         out = torch.empty(rows, n, dtype=torch.float16, device=xq.device)
         capi.check(self.lib.wush_comm_gemv_allreduce(self.comm, xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(),
