@@ -31,6 +31,8 @@
 //     instructions on column pairs); 1/256 is applied once at the end.
 //
 // Algorithmic HBM bytes: 9*N*K/16 (weights) + 9*M*K/16 (activations, L2 resident) + 2*M*N.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "peer_common.cuh"
 #include "tc_common.cuh"
@@ -41,6 +43,8 @@ namespace wush {
 __device__ int g_device_flag;                       // library-owned error word of the streaming kernels
 
 namespace {
+
+namespace cg = cooperative_groups;
 
 constexpr int ST_KS = 4;                            // groups per code stage (64 B of codes per row, 64-byte swizzle)
 constexpr int ST_SG = 8;                            // groups per scale tile (16 B per row): one per two code stages
@@ -57,8 +61,10 @@ constexpr float MAGIC = 12582912.0f;
 // `sslots` pairs later; sslots >= (stages + 1) / 2 makes the code ring's empty barriers
 // sufficient to protect it.
 struct StreamPlan {
-    int rows, xc, stage, stages, scales, sx, sslot, sslots, prep, pslot, pscale, bars, total, tx_codes, tx_scales;
-    __host__ __device__ StreamPlan(int warps, int xrows) {
+    int rows, xc, stage, stages, scales, sx, sslot, sslots, prep, pslot, pscale, bars, red, total, tx_codes, tx_scales;
+    // ksplit: the CTA is one of a cluster that shares its rows and splits K; a smaller ring so that
+    // four CTAs fit a multiprocessor, and room for the fp32 partial results handed to the leader
+    __host__ __device__ StreamPlan(int warps, int xrows, bool ksplit = false) {
         rows = warps * 16;
         xc = ((rows * 64 + 1023) / 1024) * 1024;             // activation codes after the weight codes
         stage = xc + ((xrows * 64 + 1023) / 1024) * 1024;
@@ -69,12 +75,14 @@ struct StreamPlan {
         pscale = ST_KS * (xrows / 8) * 32 * 8;
         pslot = pscale + ST_KS * (xrows / 8) * 4 * 8;
         stages = ST_MAX_STAGES;
-        while (stages > 2 && stages * (stage + pslot) + ((stages + 2) / 2) * sslot > 100 * 1024) --stages;   // two CTAs per SM
+        const int budget = ksplit ? 44 * 1024 : 100 * 1024;   // two CTAs per SM, four of a split cluster
+        while (stages > 2 && stages * (stage + pslot) + ((stages + 2) / 2) * sslot > budget) --stages;
         sslots = (stages + 2) / 2;
         scales = stages * stage;
         prep = scales + sslots * sslot;
         bars = prep + stages * pslot;
-        total = bars + 3 * ST_MAX_STAGES * 8 + 1024;          // + slack for the 1 KB alignment
+        red = bars + 3 * ST_MAX_STAGES * 8 + 64;              // 16-byte aligned: bars is a multiple of 128
+        total = red + (ksplit ? warps * (xrows / 8) * 32 * 16 : 0) + 1024;   // + slack for the 1 KB alignment
         tx_codes = rows * 64 + xrows * 64;
         tx_scales = rows * 16 + xrows * 16;
     }
@@ -105,8 +113,12 @@ __device__ __forceinline__ float scale_of(const uint2& v, int e) {
 // PUSH (one block of rows, gridDim.y == 1): instead of y the result goes into slot (step & 1, rank)
 // of EVERY rank's exchange buffer, stored over NVLink from the epilogue; the CTA's last compute warp
 // counts the CTA and the grid's last CTA publishes the step (peer_common.cuh).
-template <int MT, bool PARTIALS, bool PUSH = false>
-__global__ void __launch_bounds__((max_warps(MT) + ST_EXTRA_WARPS) * 32, 2)
+// KSPLIT: launched as clusters of S CTAs along z that own the same rows and 1/S of K each; the
+// partial sums of ranks 1..S-1 travel through distributed shared memory to rank 0, which adds them
+// in rank order and writes the result.  Every thread of every CTA reaches both cluster barriers,
+// whatever its role and whether or not one of its bounded waits gave up.
+template <int MT, bool PARTIALS, bool PUSH = false, bool KSPLIT = false>
+__global__ void __launch_bounds__(KSPLIT ? (4 + ST_EXTRA_WARPS) * 32 : (max_warps(MT) + ST_EXTRA_WARPS) * 32, KSPLIT ? 4 : 2)
 w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_constant__ CUtensorMap map_xq,
                    const __grid_constant__ CUtensorMap map_ws, const __grid_constant__ CUtensorMap map_xs,
                    __half* __restrict__ y, int32_t* __restrict__ part, int M, int N, int K, int warps,
@@ -114,7 +126,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
 {
     __shared__ unsigned int s_warps_done;
     constexpr int XROWS = MT * 8;
-    const StreamPlan L(warps, XROWS);
+    const StreamPlan L(warps, XROWS, KSPLIT);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
@@ -122,8 +134,18 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
     uint64_t* xready = empty + ST_MAX_STAGES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = K >> 5, n_chunks = G / ST_KS;
+    const int G = K >> 5;
+    int n_chunks = G / ST_KS, kc0 = 0, crank = 0, csize = 1;
+    if constexpr (KSPLIT) {
+        cg::cluster_group cluster = cg::this_cluster();
+        crank = (int)cluster.block_rank();
+        csize = (int)cluster.num_blocks();
+        n_chunks /= csize;                                   // the host made this an even number of whole chunks
+        kc0 = crank * n_chunks;
+    }
     const int n_base = blockIdx.x * L.rows, m_base = blockIdx.y * XROWS;
+    float2 acc[MT][2];                                   // [m-tile][row gid | row gid+8] x (col 2tig, 2tig+1)
+    bool ok = true;
 
     if (tid == 0) {
         for (int i = 0; i < L.stages; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], warps); tc::mbar_init(&xready[i], 1); }
@@ -146,12 +168,12 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
                 uint8_t* st = smem + slot * L.stage;
                 const bool with_scales = (kc & 1) == 0;
                 tc::mbar_expect_tx(&full[slot], L.tx_codes + (with_scales ? L.tx_scales : 0));
-                tc::tma_load_2d(st, &map_wq, &full[slot], kc * 64, n_base);
-                tc::tma_load_2d(st + L.xc, &map_xq, &full[slot], kc * 64, m_base);
+                tc::tma_load_2d(st, &map_wq, &full[slot], (kc0 + kc) * 64, n_base);
+                tc::tma_load_2d(st + L.xc, &map_xq, &full[slot], (kc0 + kc) * 64, m_base);
                 if (with_scales) {
                     uint8_t* sc = smem + L.scales + sslot * L.sslot;
-                    tc::tma_load_2d(sc, &map_ws, &full[slot], (kc >> 1) * ST_SG, n_base);
-                    tc::tma_load_2d(sc + L.sx, &map_xs, &full[slot], (kc >> 1) * ST_SG, m_base);
+                    tc::tma_load_2d(sc, &map_ws, &full[slot], ((kc0 + kc) >> 1) * ST_SG, n_base);
+                    tc::tma_load_2d(sc + L.sx, &map_xs, &full[slot], ((kc0 + kc) >> 1) * ST_SG, m_base);
                     if (++sslot == L.sslots) sslot = 0;
                 }
                 ++issued;
@@ -165,9 +187,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
                         if (tc::mbar_try_wait(&full[i], 0) || tc::mbar_try_wait(&full[i], 1)) break;
             }
         }
-        return;
-    }
-    if (warp == warps + 1) {
+    } else if (warp == warps + 1) {
         // ------------------------------ activation prep ------------------------------------------
         // Every compute warp needs the same activation fragments and scales; this warp widens the
         // nibbles and converts the bf16 scales ONCE per stage into MMA-fragment order so that the
@@ -176,7 +196,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
             int slot = 0, sslot = 0;
             uint32_t phase = 0;
             for (int kc = 0; kc < n_chunks; ++kc) {
-                if (!tc::mbar_wait(&full[slot], phase)) { if (lane == 0) atomicExch(&g_device_flag, 3); return; }
+                if (!tc::mbar_wait(&full[slot], phase)) { if (lane == 0) atomicExch(&g_device_flag, 3); break; }
                 const uint8_t* xc = smem + slot * L.stage + L.xc;
                 const uint8_t* sc = smem + L.scales + sslot * L.sslot + L.sx + (kc & 1) * 8;
                 uint2* frag = reinterpret_cast<uint2*>(smem + L.prep + slot * L.pslot);
@@ -201,23 +221,21 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
                 if ((kc & 1) && ++sslot == L.sslots) sslot = 0;
             }
         }
-        return;
     }
-    if (warp > warps) return;
-
-    // ---------------------------------- compute warps -------------------------------------------
+    if constexpr (!KSPLIT) {
+        if (warp >= warps) return;
+    }
     const int gid = lane >> 2, tig = lane & 3;
-    float2 acc[MT][2];                                   // [m-tile][row gid | row gid+8] x (col 2tig, 2tig+1)
+    if (!KSPLIT || warp < warps) {
+    // ---------------------------------- compute warps -------------------------------------------
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = make_float2(0.f, 0.f);
-
     // ldmatrix row addresses (the 128-byte swizzle XORs the 16-byte piece index with row & 7)
     const int w_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);        // matrices 0/2: rows 0-7, 1/3: rows 8-15
     const int w_gsel = lane >> 4;                                             // matrices 2,3 take the next group
     const int swz = ((lane >> 1) & 3) << 4;             // 64-byte swizzle: piece index ^= (row >> 1) & 3
     int slot = 0, sslot = 0;
     uint32_t phase = 0;
-    bool ok = true;
     for (int kc = 0; kc < n_chunks; ++kc) {
         if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
         if constexpr (!PARTIALS) {
@@ -276,7 +294,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
                         }
                         mma_s8_biased(d, a0, a1, a2, a3, b0, b1);
                         if constexpr (PARTIALS) {
-                            const int g = kc * ST_KS + gq + e;
+                            const int g = (kc0 + kc) * ST_KS + gq + e;
                             const int na = n_base + warp * 16 + gid, nb = na + 8;
                             const int m0 = m_base + mt * 8 + tig * 2, m1 = m0 + 1;
                             if (m0 < M && na < N) part[((size_t)m0 * N + na) * G + g] = (int32_t)(d[0] - MAGIC_BITS) >> 8;
@@ -299,9 +317,34 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
         if (++slot == L.stages) { slot = 0; phase ^= 1; }
         if ((kc & 1) && ++sslot == L.sslots) sslot = 0;
     }
-    if (!ok) {
-        if (lane == 0) atomicExch(&g_device_flag, 2);
-        if constexpr (!PUSH) return;                          // PUSH: still count the CTA, the peers wait for the flag
+    if (!ok && lane == 0) atomicExch(&g_device_flag, 2);
+    }   // roles
+
+    if constexpr (KSPLIT) {
+        cg::cluster_group cluster = cg::this_cluster();
+        float4* red = reinterpret_cast<float4*>(smem + L.red);
+        if (warp < warps && crank != 0) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                red[(warp * MT + mt) * 32 + lane] = make_float4(acc[mt][0].x, acc[mt][0].y, acc[mt][1].x, acc[mt][1].y);
+        }
+        cluster.sync();
+        if (warp < warps && crank == 0) {
+            for (int r = 1; r < csize; ++r) {
+                const float4* other = cluster.map_shared_rank(red, r);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const float4 v = other[(warp * MT + mt) * 32 + lane];
+                    acc[mt][0].x += v.x; acc[mt][0].y += v.y; acc[mt][1].x += v.z; acc[mt][1].y += v.w;
+                }
+            }
+        }
+        cluster.sync();                                       // the partials are read: the other CTAs may leave
+        if (crank != 0) return;
+    }
+    if (warp >= warps) return;
+    if constexpr (!PUSH) {
+        if (!ok) return;                                      // PUSH: still count the CTA, the peers wait for the flag
     }
     if constexpr (PUSH) {
         const int na = n_base + warp * 16 + gid, nb = na + 8;
@@ -356,6 +399,21 @@ int pick_warps(int64_t N, int64_t m_blocks, int limit)
     return (int)w;
 }
 
+// K split over a cluster of CTAs.  A narrow layer has fewer 16-row blocks than the machine has warp
+// schedulers (4 per multiprocessor), and every CTA walks the whole K alone -- its compute warps and
+// its activation-prep warp alike -- so the time is that serial walk, not the weight stream.  Splitting
+// K over 2, 4 or 8 CTAs shortens the walk and fills the schedulers.  Whole scale tiles (two chunks)
+// per rank, and at least 8 chunks each.
+int pick_split(int64_t N, int64_t m_blocks, int64_t K)
+{
+    // measured (us, no split / 2 / 4 / 8): N=8192 K=8192 M=32: 47 / 35 / 29 / 36, M=64: 54 / 48 / 52 / 62,
+    // M=128: 74 / 84 / 91 / 109; N=4096 K=12288 M=32: 60 / 39 / 29 / 26; N=24576 K=4096 M=32: 37 / 42 / 46 / 61
+    const int64_t compute_warps = ((N + 15) / 16) * m_blocks, chunks = K / 128, sms = sm_count();
+    int s = compute_warps <= 2 * sms ? 8 : compute_warps <= 4 * sms ? 4 : compute_warps < 8 * sms ? 2 : 1;
+    while (s > 1 && (chunks % (2 * s) != 0 || chunks < 8 * s)) s >>= 1;
+    return s;
+}
+
 template <int MT, bool PARTIALS, bool PUSH = false>
 int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
                   void* y, int32_t* part, cudaStream_t st, const PeerTable& peers = PeerTable{})
@@ -363,8 +421,10 @@ int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const vo
     constexpr int XROWS = MT * 8;
     const int64_t m_blocks = (M + XROWS - 1) / XROWS;
     if (m_blocks > 65535) return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode): M too large");
-    const int warps = pick_warps(N, m_blocks, max_warps(MT));
-    const StreamPlan L(warps, XROWS);
+    const int split = PARTIALS ? 1 : pick_split(N, m_blocks, K);
+    // split clusters: four CTAs of at most four compute warps per multiprocessor
+    const int warps = split > 1 ? pick_warps(N, m_blocks * split / 2, 4) : pick_warps(N, m_blocks, max_warps(MT));
+    const StreamPlan L(warps, XROWS, split > 1);
     CUtensorMap mwq, mxq, mws, mxs;
     int s;
     if ((s = make_map_2d(&mwq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 64, L.rows, CU_TENSOR_MAP_SWIZZLE_64B))) return s;
@@ -373,6 +433,27 @@ int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const vo
     if ((s = make_map_2d(&mxs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, K / 32, M, ST_SG, XROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
     dim3 grid((unsigned)((N + L.rows - 1) / L.rows), (unsigned)m_blocks);
     if (PUSH && grid.y != 1) return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode, pushed): one block of rows only");
+    if constexpr (!PARTIALS) {
+        if (split > 1) {
+            grid.z = (unsigned)split;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3((warps + ST_EXTRA_WARPS) * 32);
+            cfg.dynamicSmemBytes = L.total;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = (unsigned)split;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t e = cudaLaunchKernelEx(&cfg, w4a4_stream_kernel<MT, false, PUSH, true>, mwq, mxq, mws, mxs, (__half*)y, part,
+                                               (int)M, (int)N, (int)K, warps, peers);
+            if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "w4a4_stream (split): %s", cudaGetErrorString(e));
+            return check_launch("w4a4_stream");
+        }
+    }
     w4a4_stream_kernel<MT, PARTIALS, PUSH><<<grid, (warps + ST_EXTRA_WARPS) * 32, L.total, st>>>(
         mwq, mxq, mws, mxs, (__half*)y, part, (int)M, (int)N, (int)K, warps, peers);
     return check_launch("w4a4_stream");
@@ -380,6 +461,10 @@ int launch_stream(const uint8_t* xq, const void* xs, const uint8_t* wq, const vo
 
 template <int MT, bool P, bool PUSH = false>
 cudaError_t set_attr() {
+    if constexpr (!P) {
+        cudaError_t e = cudaFuncSetAttribute(w4a4_stream_kernel<MT, P, PUSH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+        if (e != cudaSuccess) return e;
+    }
     return cudaFuncSetAttribute(w4a4_stream_kernel<MT, P, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
 }
 
