@@ -196,6 +196,20 @@ def test_gemm_tile_tcgen05_vs_fp64(dev, orc, shape):
     _assert_close(y3, y64, shape)
 
 
+@pytest.mark.parametrize("shape", [(8, 264, 8192), (32, 1000, 8192), (20, 2048, 2048), (5, 520, 1024), (70, 776, 4096)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_decode_split_k_vs_fp64(dev, orc, shape):
+    """Narrow layers: the streaming kernel splits K over a cluster of 8 / 8 / 2 / 1 / 4 CTAs and sums
+    the partial results through distributed shared memory; ragged rows and row blocks included."""
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=7 * M + N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    y = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_DECODE)
+    _assert_close(y, y64, shape)
+    y2 = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_DECODE)
+    assert torch.equal(y, y2)                                              # fixed summation order
+
+
 def test_f16_route_wide_scale_range(dev, orc):
     """Rows whose group scales span many octaves (and exact-zero groups) through the fp16-folded route."""
     g = torch.Generator().manual_seed(5)
