@@ -115,13 +115,10 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
         // the layer, the fp16 route has a floor of one tile per multiprocessor over the whole K.  Times in
         // microseconds from measurements on the 70B gate+up layer (4.7e8 weights) and on narrow layers.
         const double elems = (double)N * (double)K, unit = elems / 4.7e8;
-        const double chain = (double)K / 128.0 * 0.38;                    // a CTA's serial walk over K
+        const auto block_us = [&](double wide) { const double t = 1.2 * wide * unit; return t > 6.0 ? t : 6.0; };
         const int64_t full_blocks = M / 32, rest = M % 32;
-        double t_stream = (double)full_blocks * (121.0 * unit > chain ? 121.0 * unit : chain);
-        if (rest) {
-            const double t = (rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : 121.0) * unit;
-            t_stream += t > chain ? t : chain;
-        }
+        double t_stream = 10.0 + (double)full_blocks * block_us(121.0);
+        if (rest) t_stream += block_us(rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : 121.0);
         const int64_t tiles = (M <= 128 ? 1 : (M + 255) / 256) * ((N + 255) / 256);
         const double waves = (double)((tiles + sm_count() - 1) / sm_count());
         const double t_f16 = waves * (double)K / 64.0 * (M <= 128 ? 0.8 : 1.05) + 30.0;
