@@ -29,6 +29,11 @@
 //         acc = fma(t, sx, acc)
 //     applies both scales with two FMAs per output and group (issued as packed fp32x2
 //     instructions on column pairs); 1/256 is applied once at the end.
+//   * Narrow layers (fewer 16-row blocks than warp schedulers) are launched as clusters of
+//     2, 4 or 8 CTAs that share their rows and split K; the partial sums reach the cluster's
+//     first CTA through distributed shared memory (pick_split, KSPLIT below).
+//   * PUSH variants write the result into the exchange buffers of all tensor-parallel ranks
+//     instead of y (peer_common.cuh).
 //
 // Algorithmic HBM bytes: 9*N*K/16 (weights) + 9*M*K/16 (activations, L2 resident) + 2*M*N.
 #include <cooperative_groups.h>
