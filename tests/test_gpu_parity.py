@@ -180,7 +180,7 @@ def _assert_close(y: torch.Tensor, y64: np.ndarray, tag):
 
 
 TILE_SHAPES = [(128, 128, 256), (256, 384, 512), (300, 504, 512), (130, 512, 4096), (33, 64, 256), (129, 8, 256),
-               (1000, 1000, 1024), (512, 4096, 4096), (2100, 264, 512)]
+               (1000, 1000, 1024), (512, 4096, 4096), (2100, 264, 512), (200, 520, 8192), (300, 1000, 4096), (100, 520, 8192)]
 
 
 @pytest.mark.parametrize("shape", TILE_SHAPES, ids=lambda s: "x".join(map(str, s)))

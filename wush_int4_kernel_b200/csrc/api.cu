@@ -90,6 +90,7 @@ int tc_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_
                 size_t, cudaStream_t);
 bool f16_supported(int64_t M, int64_t N, int64_t K);
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int f16_fused_split(int64_t M, int64_t N, int64_t K);
 int f16_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
                  size_t, cudaStream_t);
 
@@ -119,9 +120,11 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
         const int64_t full_blocks = M / 32, rest = M % 32;
         double t_stream = 10.0 + (double)full_blocks * block_us(121.0);
         if (rest) t_stream += block_us(rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : 121.0);
-        const int64_t tiles = (M <= 128 ? 1 : (M + 255) / 256) * ((N + 255) / 256);
-        const double waves = (double)((tiles + sm_count() - 1) / sm_count());
-        const double t_f16 = waves * (double)K / 64.0 * (M <= 128 ? 0.8 : 1.05) + 30.0;
+        const int split = f16_fused_split(M, N, K);                   // K ranges: the 256-row kernel, also for M <= 128
+        const bool wide = M > 128 || split > 1;
+        const int64_t units = (wide ? (M + 255) / 256 : 1) * ((N + 255) / 256) * split;
+        const double waves = (double)((units + sm_count() - 1) / sm_count());
+        const double t_f16 = waves * (double)K / 64.0 / split * (wide ? 1.05 : 0.8) + 30.0 + (split > 1 ? 8.0 : 0.0);
         return t_stream <= t_f16 ? WUSH_GEMM_DECODE : WUSH_GEMM_TILE_F16;
     }
     if (M >= 128 && f16_ok) return WUSH_GEMM_TILE_F16;

@@ -379,10 +379,15 @@ constexpr int R_BOFF = R_STAGES * R_STAGE;
 constexpr int R_BARS = R_BOFF + R_BUFS * QB_BYTES;
 constexpr int R_TOTAL = R_BARS + (2 * R_STAGES + 2 * R_BUFS + 2 * F_ACC + 1) * 8 + 16 + 1024;
 
+//
+// Split K (ksplit > 1, few tiles on many multiprocessors): the unit of work is (tile, K range); a unit's
+// scaled fp32 results go to part[range][M][N] instead of y and splitk_reduce_kernel adds the ranges in
+// order.  A range is a whole number of 16-byte scale vectors (4 stages).
 __global__ void __launch_bounds__(R_THREADS, 1)
 gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
                       const unsigned short* __restrict__ ws, const float* __restrict__ down, const TileScale sc,
-                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err, int ksplit,
+                      float* __restrict__ part)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -396,8 +401,8 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
-    const int k_steps = K / 64, G = K >> 5;
+    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN, n_units = tiles_m * tiles_n * ksplit;
+    const int k_steps = K / 64 / ksplit, G = K >> 5;               // stages per unit
 
     if (tid == 0) {
         for (int i = 0; i < R_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 17); }
@@ -421,9 +426,10 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t slot = 0, phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int t = u / ksplit, ks0 = (u % ksplit) * k_steps;
                 const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
-                for (int ks = 0; ks < k_steps; ++ks) {
+                for (int ks = ks0; ks < ks0 + k_steps; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
                     uint8_t* st = smem + slot * R_STAGE;
                     tc::mbar_expect_tx(&full[slot], RA_BYTES + QP_BYTES);
@@ -445,7 +451,7 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t slot = 0, phase = 0, buf = 0, bphase = 0, aphase = 0;
             const uint32_t idesc = tc::idesc_f16(FN);
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 if (!tc::mbar_wait(&acc_empty[0], aphase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
@@ -477,18 +483,19 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const int d = (tid - 256) & 255, g = (tid - 256) >> 8;     // weight row of the tile, group of the stage
         uint32_t slot = 0, phase = 0, buf = 0, bphase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const int t = u / ksplit, ks0 = (u % ksplit) * k_steps, ks1 = ks0 + k_steps;   // ks0 is a multiple of 4
             const int n = (t / tiles_m) * FN + d;
             const bool live = n < N;
             const float dn = live ? down[n] : 0.f;
             // scales: one 16-byte load covers this row's 8 groups = 4 stages; the next one is in flight meanwhile
             const uint4* srow = reinterpret_cast<const uint4*>(ws + (size_t)(live ? n : 0) * G);
             const uint4 zero4 = make_uint4(0, 0, 0, 0);
-            uint4 s_cur = zero4, s_nxt = live ? __ldg(srow) : zero4;
-            for (int ks = 0; ks < k_steps; ++ks) {
+            uint4 s_cur = zero4, s_nxt = live ? __ldg(srow + (ks0 >> 2)) : zero4;
+            for (int ks = ks0; ks < ks1; ++ks) {
                 if ((ks & 3) == 0) {
                     s_cur = s_nxt;
-                    if (live && ks + 4 < k_steps) s_nxt = __ldg(srow + (ks >> 2) + 1);
+                    if (live && ks + 4 < ks1) s_nxt = __ldg(srow + (ks >> 2) + 1);
                 }
                 const uint32_t pair = (ks & 2) ? ((ks & 1) ? s_cur.w : s_cur.z) : ((ks & 1) ? s_cur.y : s_cur.x);   // groups 2ks, 2ks+1
                 const float s_f = g ? bf16_hi(pair) : bf16_lo(pair);
@@ -520,8 +527,10 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const uint32_t ab = (uint32_t)upper;                            // column block of this half's accumulator
         uint32_t aphase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const int t = u / ksplit;
             const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
+            float* prow = part + ((size_t)(u % ksplit) * M + (m0 + row < M ? m0 + row : 0)) * N;   // ksplit > 1 only
             if (!tc::mbar_wait(&acc_full[0], aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -545,6 +554,15 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
                             const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
                             const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                            if (ksplit > 1) {
+                                float r[8];
+#pragma unroll
+                                for (int p = 0; p < 8; ++p) r[p] = __uint_as_float(v[v8 * 8 + p]) * (fm * fs[p]);
+                                float4* dst = reinterpret_cast<float4*>(prow + n + v8 * 8);
+                                dst[0] = make_float4(r[0], r[1], r[2], r[3]);
+                                dst[1] = make_float4(r[4], r[5], r[6], r[7]);
+                                continue;
+                            }
                             uint32_t o[4];
 #pragma unroll
                             for (int p = 0; p < 4; ++p) {
@@ -743,6 +761,24 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
+// y = fp16(sum over the K ranges, in order, of the fp32 partial results); 8 outputs per thread
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float4* __restrict__ part, uint4* __restrict__ y, long long n_vec, int ksplit)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    float4 a = part[2 * i], b = part[2 * i + 1];
+    for (int s = 1; s < ksplit; ++s) {
+        const float4 c = part[2 * (s * n_vec + i)], d = part[2 * (s * n_vec + i) + 1];
+        a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+        b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+    }
+    const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+    const __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
+    y[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                      *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+}
+
 }  // namespace
 
 int f16_set_attributes()
@@ -765,16 +801,37 @@ bool f16_supported(int64_t M, int64_t N, int64_t K) { return M >= 1 && K % 64 ==
 constexpr int64_t FUSED_MAX_ROWS = 2048;
 static bool use_fused(int64_t M, int64_t N, int64_t K) { return M <= FUSED_MAX_ROWS && K % 256 == 0; }   // whole 16-byte scale vectors
 
+// K ranges of the 256-row in-kernel-widening kernel: as many as keep every multiprocessor busy when the
+// tiles alone would not (N = 8192, M = 256: 32 tiles), each a whole number of scale vectors and at least
+// 16 stages long.  More than one range also sends M <= 128 to the 256-row kernel (half-empty tiles, but
+// all multiprocessors at work).
+int f16_fused_split(int64_t M, int64_t N, int64_t K)
+{
+    if (!use_fused(M, N, K)) return 1;
+    const int64_t tiles = ((M + 2 * FM - 1) / (2 * FM)) * ((N + FN - 1) / FN), stages = K / 64;
+    int s = 1;
+    while (s < 8 && tiles * s * 2 <= sm_count()) s *= 2;
+    while (s > 1 && (stages % (4 * s) != 0 || stages / s < 16)) s >>= 1;
+    return s;
+}
+
 // scratch: error word | fp16 activations (M x K) | [fp16 weights (N x K), unless widened in-kernel] |
-// 2^e per row of each | 2^-e per weight row
-size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
+// 2^e per row of each | 2^-e per weight row | [fp32 partial results of the K ranges]
+// The _min form leaves the partial results out: with that much the product runs without the K split.
+size_t f16_workspace_bytes_min(int64_t M, int64_t N, int64_t K)
 {
     const size_t w16 = use_fused(M, N, K) ? 0 : align256((size_t)N * K * 2);
     return 256 + align256((size_t)M * K * 2) + w16 + align256((size_t)M * 4) + 2 * align256((size_t)N * 4);
 }
 
+size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    const int split = f16_fused_split(M, N, K);
+    return f16_workspace_bytes_min(M, N, K) + (split > 1 ? align256((size_t)split * M * N * 4) : 0);
+}
+
 static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N,
-                              int64_t K, void* y, void* workspace, cudaStream_t st)
+                              int64_t K, void* y, void* workspace, size_t workspace_bytes, cudaStream_t st)
 {
     uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
     int* err = reinterpret_cast<int*>(base);
@@ -782,6 +839,9 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     float* fa = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + align256((size_t)M * K * 2));
     float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
     float* dn = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fb) + align256((size_t)N * 4));
+    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dn) + align256((size_t)N * 4));
+    int split = f16_fused_split(M, N, K);
+    if (workspace_bytes < f16_workspace_bytes(M, N, K) || !aligned16(y)) split = 1;   // scratch without room for the partial results
     cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
     dequant_f16_kernel<true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
@@ -789,17 +849,25 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     if (int s = check_launch("f16 pre-pass")) return s;
     CUtensorMap ma, mp;
     int s;
-    const bool wide = M > FM;                                          // more than one 128-row tile: 256-row tiles
+    const bool wide = M > FM || split > 1;                             // 256-row tiles: more than one 128-row tile, or K ranges
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, wide ? 2 * FM : FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     if ((s = make_map_2d(&mp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 32, FN, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
     const int tile_rows = wide ? 2 * FM : FM;
     const int64_t tiles = ((M + tile_rows - 1) / tile_rows) * ((N + FN - 1) / FN);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const int64_t units = wide ? tiles * split : tiles;
+    const int grid = (int)(units < sm_count() ? units : sm_count());
     const TileScale sc = {fa, fb, 0.f, nullptr};
-    if (wide)
+    if (wide) {
         gemm_f16_fused2_kernel<<<grid, R_THREADS, R_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M,
-                                                                 (int)N, (int)K, err);
-    else
+                                                                 (int)N, (int)K, err, split, part);
+        if (split > 1) {
+            if (int s2 = check_launch("gemm_f16_fused")) return s2;
+            const long long n_vec = (long long)M * N / 8;
+            splitk_reduce_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float4*>(part),
+                                                                                reinterpret_cast<uint4*>(y), n_vec, split);
+            return check_launch("splitk_reduce");
+        }
+    } else
         gemm_f16_fused_kernel<<<grid, Q_THREADS, Q_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N,
                                                                 (int)K, err);
     return check_launch("gemm_f16_fused");
@@ -810,11 +878,11 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
 {
     if (!aligned16(y) || !aligned16(workspace))
         return fail(WUSH_ERR_INVALID_ARGUMENT, "w4a4_gemm(f16): output and workspace must be 16-byte aligned");
-    if (workspace_bytes < f16_workspace_bytes(M, N, K))
+    if (workspace_bytes < f16_workspace_bytes_min(M, N, K))
         return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, %zu given",
-                    f16_workspace_bytes(M, N, K), workspace_bytes);
+                    f16_workspace_bytes_min(M, N, K), workspace_bytes);
     if (use_fused(M, N, K) && aligned16(ws))
-        return f16_fused_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, st);
+        return f16_fused_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
     uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
     int* err = reinterpret_cast<int*>(base);
     __half* a16 = reinterpret_cast<__half*>(base + 256);
@@ -964,7 +1032,7 @@ WUSH_API int wush_w4a4_gemm_static_scratch(const uint8_t* xq, const void* xs, co
     if (!f16_supported(M, N, K))
         return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm_static_scratch: needs K %% 64 == 0 and N %% 8 == 0 (got K=%lld, N=%lld)",
                     (long long)K, (long long)N);
-    const size_t need = f16_workspace_bytes(M, N, K);
+    const size_t need = f16_workspace_bytes_min(M, N, K);
     if (need > (size_t)WUSH_STATIC_SCRATCH_BYTES)
         return fail(WUSH_ERR_WORKSPACE,
                     "w4a4_gemm_static_scratch: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in array holds %zu; "
