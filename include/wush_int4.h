@@ -100,7 +100,7 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  *   WUSH_GEMM_AUTO     : pick by shape (GEMV for M <= 2, and for M <= 4 on narrow layers;
  *                        DECODE up to 32 rows; for 32 < M <= 512 the cheaper of DECODE in
  *                        32-row blocks and TILE_F16 by a measured cost estimate in N, K and
- *                        M; TILE_F16 beyond; TILE only where neither takes K)
+ *                        M; TILE_F16 beyond; the exact-sum TILE variant only on request)
  *   WUSH_GEMM_GEMV     : CUDA-core streaming kernel (M <= 4)
  *   WUSH_GEMM_DECODE   : tensor-core streaming kernel, weights as the wide operand (any M)
  *   WUSH_GEMM_TILE     : tcgen05 kind::i8 tile GEMM, exact int32 sum per group (any M)
@@ -120,6 +120,9 @@ typedef enum {
     WUSH_GEMM_TILE_F16 = 4
 } wush_gemm_variant;
 size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
+/* The variant WUSH_GEMM_AUTO stands for on the current device for this shape (one of the other
+ * four values): what wush_w4a4_gemm and wush_w4a4_gemm_workspace_bytes resolve it to. */
+int wush_w4a4_gemm_pick_variant(int64_t M, int64_t N, int64_t K);
 int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws,
                    int64_t M, int64_t N, int64_t K, void* y, int variant, void* workspace,
                    size_t workspace_bytes, void* stream);

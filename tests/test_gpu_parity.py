@@ -210,6 +210,23 @@ def test_decode_split_k_vs_fp64(dev, orc, shape):
     assert torch.equal(y, y2)                                              # fixed summation order
 
 
+def test_auto_variant_by_shape(dev):
+    """What AUTO stands for: the GEMV for one or two rows, the streaming kernel for decode batches and for
+    mid-size M on narrow layers, the fp16 route where its tiles (or K ranges) fill the machine."""
+    lib = capi.load()
+    pick = lib.wush_w4a4_gemm_pick_variant
+    assert pick(1, 57344, 8192) == capi.GEMM_GEMV and pick(2, 8192, 8192) == capi.GEMM_GEMV
+    assert pick(4, 57344, 8192) == capi.GEMM_DECODE and pick(4, 8192, 8192) == capi.GEMM_GEMV
+    assert pick(16, 57344, 8192) == capi.GEMM_DECODE and pick(32, 24576, 4096) == capi.GEMM_DECODE
+    assert pick(64, 8192, 8192) == capi.GEMM_DECODE and pick(128, 8192, 3584) == capi.GEMM_DECODE
+    assert pick(128, 57344, 8192) == capi.GEMM_TILE_F16 and pick(256, 8192, 8192) == capi.GEMM_TILE_F16
+    assert pick(4096, 57344, 8192) == capi.GEMM_TILE_F16
+    assert pick(48, 64, 96) == capi.GEMM_DECODE                   # K no tile kernel takes: the generic decode path
+    for shape in [(1, 64, 64), (300, 1000, 4096), (96, 24576, 4096)]:
+        v = pick(*shape)
+        assert lib.wush_w4a4_gemm_workspace_bytes(*shape, capi.GEMM_AUTO) == lib.wush_w4a4_gemm_workspace_bytes(*shape, v)
+
+
 def test_f16_route_wide_scale_range(dev, orc):
     """Rows whose group scales span many octaves (and exact-zero groups) through the fp16-folded route."""
     g = torch.Generator().manual_seed(5)

@@ -28,6 +28,7 @@ SIGNATURES = {
     "wush_fused_transform_quant_int4": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "wush_fused_silu_mul_transform_quant_int4": (_int, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "wush_w4a4_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "wush_w4a4_gemm_pick_variant": (_int, [_i64, _i64, _i64]),
     "wush_w4a4_gemm": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp, _sz, _vp]),
     "wush_w4a4_gemm_static_scratch_limit": (_sz, []),
     "wush_w4a4_gemm_static_scratch": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),

@@ -152,6 +152,11 @@ WUSH_API size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, 
     return 0;
 }
 
+WUSH_API int wush_w4a4_gemm_pick_variant(int64_t M, int64_t N, int64_t K)
+{
+    return wush::resolve_variant(WUSH_GEMM_AUTO, M, N, K);
+}
+
 WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M,
                             int64_t N, int64_t K, void* y, int variant, void* workspace, size_t workspace_bytes,
                             void* stream)
