@@ -16,6 +16,12 @@ Prints ONE JSON line: metric effective TOPS (2*M*N*K / time), plus
   cpu_baseline  the CPU oracle port of the same layer on this box's host cores
   e2e           the same metric through the public ops with HOST activations and results
   clocks        SM clock / throttle reasons sampled with nvidia-smi while the step runs
+  prefill       the other half of the metric, measured in the same run: M=4096 rows through the same
+                layer (this rank's column shard at N GPUs), against the tensor-core peak
+  ffn_block     (N > 1 only) the tensor-parallel FFN block 8192 -> 2 x 28672 -> 8192 at M = 1 / 32 / 2048:
+                with the exchange over NVLink peer memory and with the NCCL all-reduce
+``config`` names the workload only and is key-for-key the same in both arms; how this arm lays the
+work out (sharding, L2 policy, timing method) is under ``setup``.
 
 ``--impl reference`` times the CPU port alone (rank 0 only): the reference's own kernels are
 sm_75-only CUDA and cannot run here, its Python path is what the oracle restates.
@@ -28,6 +34,7 @@ import math
 import os
 import statistics
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -39,6 +46,15 @@ L2_BYTES = 126 * 1024 * 1024
 # capture summarised in profiles/gemv_dp4a_decode_m1_k8192_n57344.md (264.27 MB read + 3.37 / 4.76 MB
 # written in the two captured launches; their mean).
 PRODUCT_KERNEL_DRAM_BYTES = 268_330_000
+PRODUCT_KERNEL_DRAM_SOURCE = ("constant from an earlier ncu capture, not measured in this run: "
+                              "profiles/gemv_dp4a_decode_m1_k8192_n57344.md (scaled by the shard's share of N)")
+INT8_NOMINAL_TOPS = 4500.0
+PREFILL_ROWS = 4096
+
+
+def workload_config(M: int) -> dict:
+    """The workload, named the same way by both arms."""
+    return {"workload": f"llama70b_gate_up_decode K={K_DIM} N={N_DIM} M={M}", "K": K_DIM, "N": N_DIM, "M": M}
 
 
 def algorithmic_bytes_product(M: int, N: int, K: int) -> int:
@@ -51,27 +67,50 @@ def algorithmic_bytes_layer(M: int, N: int, K: int) -> int:
     return 2 * M * K + 64 * K + 2 * (9 * M * K // 16) + 9 * N * K // 16 + 2 * M * N
 
 
-def measured_hbm_peak():
+def measured_peak(key: str, fallback: float):
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+            return float(json.load(f)[key]), "measured"
     except (OSError, KeyError, ValueError):
-        return 6650.0, "fallback"
+        return fallback, "fallback"
+
+
+def measured_hbm_peak():
+    return measured_peak("hbm_gbs", 6650.0)
 
 
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the layer (test infrastructure, the only place outside tests and
 # the smoke check where oracle/ is executed)
 # ---------------------------------------------------------------------------------------------
-def cpu_layer_inputs(M: int, n_rows: int, seed: int = 0):
+CPU_BLOCK_ROWS = 4096
+
+
+def cpu_layer_inputs(M: int, n_rows: int, seed: int = 1234):
+    """The seeded synthetic layer of synth.py, drawn on the CPU: activations N(0,1) with 0.5 % of the
+    channels x 20, weights N(0, 0.02), transform solved from 512 calibration rows, weights transformed
+    and sigma-clip quantised.  One block of CPU_BLOCK_ROWS weight rows is built this way and repeated
+    up to n_rows (building all 57344 rows in fp64 on the host would take longer than the timed
+    sample itself; the CPU path's time does not depend on the values)."""
     import numpy as np
-    rng = np.random.default_rng(seed)
-    G = K_DIM // 32
-    wq = rng.integers(0, 256, (n_rows, K_DIM // 2), dtype=np.uint8)
-    ws = np.full((n_rows, G), 0x3C24, np.uint16)                      # bf16 0.01
-    x = (rng.standard_normal((M, K_DIM)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
-    t = (np.tile(np.eye(32, dtype=np.float32), (G, 1, 1)).view(np.uint32) >> 16).astype(np.uint16)
+    import torch
+
+    from oracle import w4a4_oracle as orc
+    from wush_int4_kernel_b200 import synth, wush_transform as wt
+
+    gen = torch.Generator().manual_seed(seed)
+    outliers = synth.outlier_channels(K_DIM, torch.Generator().manual_seed(7))
+    x_cal = synth.draw_activations(synth.CALIB_ROWS, K_DIM, outliers, gen).float()
+    block = min(CPU_BLOCK_ROWS, n_rows)
+    w = (0.02 * torch.randn(block, K_DIM, generator=gen)).to(torch.bfloat16)
+    t64 = wt.solve_from_grams(wt.diag_block_gram(x_cal) / synth.CALIB_ROWS, wt.diag_block_gram(w) / block)
+    wq_b, ws_b = orc.quant_int4(orc.bits(wt.transform_weights(w, t64).to(torch.bfloat16).contiguous()))
+    reps = -(-n_rows // block)
+    wq = np.ascontiguousarray(np.tile(wq_b, (reps, 1))[:n_rows])
+    ws = np.ascontiguousarray(np.tile(ws_b, (reps, 1))[:n_rows])
+    x = orc.bits(synth.draw_activations(M, K_DIM, outliers, gen))
+    t = orc.bits(t64.to(torch.bfloat16).contiguous())
     return x, t, wq, ws
 
 
@@ -86,11 +125,11 @@ def cpu_model() -> str:
     return "unknown"
 
 
-def time_cpu_layer(M: int, n_rows: int, steps: int, warmup: int):
+def time_cpu_layer(M: int, n_rows: int, steps: int, warmup: int, inputs=None):
     from oracle import w4a4_oracle as orc
     cores = os.cpu_count() or 1
     orc.set_threads(cores)
-    x, t, wq, ws = cpu_layer_inputs(M, n_rows)
+    x, t, wq, ws = inputs if inputs is not None else cpu_layer_inputs(M, n_rows)
     for _ in range(warmup):
         orc.layer(x, t, wq, ws)
     times = []
@@ -108,19 +147,95 @@ def run_reference_arm(args):
     M = args.rows
     n_rows = N_DIM                                   # the whole layer: ~0.5 G MAC per row of X
     times, cores = time_cpu_layer(M, n_rows, args.steps, args.warmup)
-    total = sum(times)
-    tops = 2.0 * M * n_rows * K_DIM * len(times) / total / 1e12
+    med = statistics.median(times)                   # the same statistic as the GPU arm's cpu_baseline leg
+    tops = 2.0 * M * n_rows * K_DIM / med / 1e12
     line = {
         "impl": "reference", "metric": "w4a4_layer_eff_tops", "value": tops, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "strong",
+        "ms_per_step": 1e3 * med, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4", "data": "synthetic",
-        "config": {"workload": f"llama70b_gate_up_decode K={K_DIM} N={N_DIM} M={M}", "K": K_DIM, "N": N_DIM, "M": M},
+        "config": workload_config(M),
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "cpu": cpu_model(), "kind": "port",
-                         "sample": f"whole layer (N={n_rows} rows of W), {len(times)} steps, OpenMP over output columns"},
+                         "sample": f"whole layer (N={n_rows} rows of W: a seeded synthetic block of {CPU_BLOCK_ROWS} rows repeated), "
+                                   f"median of {len(times)} steps (mean {1e3 * sum(times) / len(times):.3f} ms), OpenMP over output columns"},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def measure_prefill(weights, t_bf16, outliers, gen, dev, world, n_local, barrier):
+    """M = PREFILL_ROWS rows through the same layer (this rank's column shard): transform+quantise, then
+    the product through the public op (my_int4._C.w4a4_gemm_s4).  Median of 5 batches of 4 graph replays
+    over the rotating weight copies, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from wush_int4_kernel_b200 import synth, timing
+    from wush_int4_kernel_b200.linear import quantise_activations, w4a4_product
+
+    M = PREFILL_ROWS
+    x = synth.draw_activations(M, K_DIM, outliers, gen)
+    xq, xs = quantise_activations(x, t_bf16)
+    use = weights[:2]
+
+    def median_ms(graphs):
+        for i in range(3):
+            graphs[i % len(graphs)].replay()
+        out = []
+        for _ in range(5):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(4):
+                graphs[i % len(graphs)].replay()
+            e1.record()
+            torch.cuda.synchronize()
+            out.append(e0.elapsed_time(e1) / 4)
+        ms = statistics.median(out)
+        if world > 1:
+            tmax = torch.tensor([ms], device=dev)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            ms = float(tmax.item())
+        return ms
+
+    layer_ms = median_ms([timing.capture(lambda wq=wq, ws=ws: w4a4_product(*quantise_activations(x, t_bf16), wq, ws))[0]
+                          for (wq, ws) in use])
+    prod_ms = median_ms([timing.capture(lambda wq=wq, ws=ws: w4a4_product(xq, xs, wq, ws))[0] for (wq, ws) in use])
+    torch.cuda.empty_cache()
+    tpeak, tkind = measured_peak("bf16_tflops", 1590.0)
+    per_gpu = 2.0 * M * n_local * K_DIM / (prod_ms * 1e-3) / 1e12
+    return {"M": M, "K": K_DIM, "N": N_DIM, "columns_per_gpu": n_local, "us_per_layer": layer_ms * 1e3,
+            "product_us": prod_ms * 1e3, "eff_tops": 2.0 * M * N_DIM * K_DIM / (layer_ms * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tpeak, "unit": "TFLOP/s", "frac": per_gpu / tpeak,
+                         "peak_kind": f"of {tkind} (cuBLAS bf16 burst; the product runs tcgen05 kind::f16 on exactly "
+                                      f"folded operands, so the dense-f16 rate is its ceiling)",
+                         "frac_of_nominal_int8": per_gpu / INT8_NOMINAL_TOPS, "kernel": "w4a4 product (per GPU)"}}
+
+
+def measure_ffn_block(world, rank, dev):
+    """hidden 8192, intermediate 28672, one rank per GPU: fused gate+up (column parallel) -> SiLU*up ->
+    transform+quantise -> down (row parallel) -> sum over ranks; once with the exchange over NVLink peer
+    memory (decode sizes; larger results fall back to NCCL inside it) and once with the NCCL all-reduce."""
+    import torch
+
+    from wush_int4_kernel_b200 import bench_matrix
+    from wush_int4_kernel_b200.peer_reduce import PeerAllReduce
+
+    layers = bench_matrix.build_ffn_layers(world, rank, dev, copies=3)
+    peer = PeerAllReduce(max_elements=64 * 8192)
+    out = {}
+    for m in (1, 32, 2048):
+        with_peer = bench_matrix.measure_ffn(m, world, rank, dev, True, peer, layers=layers)
+        with_nccl = bench_matrix.measure_ffn(m, world, rank, dev, True, None, layers=layers)
+        out[str(m)] = {"us_peer_memory": with_peer["us_per_block"], "exchange": with_peer["all_reduce"],
+                       "us_nccl": with_nccl["us_per_block"], "graph": with_peer["graph"] and with_nccl["graph"],
+                       "eff_tops_whole_block": with_peer["eff_tops_whole_block"]}
+        torch.cuda.empty_cache()
+    err = peer.error()
+    peer.close()
+    out["peer_wait_timeout"] = bool(err)
+    out["block"] = "ffn 8192 -> 2 x 28672 -> 8192, tensor parallel over %d GPUs" % world
+    return out
 
 
 # ---------------------------------------------------------------------------------------------
@@ -150,25 +265,43 @@ def run_gpu_arm(args):
     n0, n1 = shard_bounds(N_DIM, world, rank, 128)
     n_local = n1 - n0
 
-    # ---- synthetic layer shard, generated on the GPU (seeded; distributions of synth.py) ----
+    # ---- synthetic layer shard (seeded; distributions of synth.py).  Built on the GPU once and kept as
+    # layer files (layer_file.py) in the temporary directory: later runs on the same box -- the other
+    # arm, the next N of a scaling series -- load the {wq, ws, T} triples instead of re-quantising them.
+    from wush_int4_kernel_b200 import layer_file, wush_transform as wt
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     outliers = synth.outlier_channels(K_DIM, torch.Generator(device=dev).manual_seed(7))
-    x_cal = synth.draw_activations(synth.CALIB_ROWS, K_DIM, outliers, gen).float()
-    from wush_int4_kernel_b200 import wush_transform as wt
-    w0 = (0.02 * torch.randn(4096, K_DIM, generator=gen, device=dev)).to(torch.bfloat16)
-    t64 = wt.solve_from_grams(wt.diag_block_gram(x_cal) / synth.CALIB_ROWS, wt.diag_block_gram(w0) / 4096)
-    t_bf16 = t64.to(torch.bfloat16).contiguous()
     shard_bytes = n_local * (K_DIM // 2 + K_DIM // 16)
     copies = max(2, -(-(2 * L2_BYTES + shard_bytes) // shard_bytes))   # consecutive steps never touch the same bytes
-    weights = []
-    for _ in range(copies):
-        wq_parts, ws_parts = [], []
-        for r0 in range(0, n_local, 8192):
-            w = (0.02 * torch.randn(min(8192, n_local - r0), K_DIM, generator=gen, device=dev)).to(torch.bfloat16)
-            q, s = _C.quant_int4(wt.transform_weights(w, t64).to(torch.bfloat16).contiguous())
-            wq_parts.append(q)
-            ws_parts.append(s)
-        weights.append((torch.cat(wq_parts).contiguous(), torch.cat(ws_parts).contiguous()))
+    cache_dir = os.path.join(tempfile.gettempdir(), "wush_w4a4_bench_layers")
+    os.makedirs(cache_dir, exist_ok=True)
+    paths = [os.path.join(cache_dir, f"gate_up_K{K_DIM}_cols{n0}-{n1}_of{N_DIM}_copy{c}_v1.pt") for c in range(copies)]
+    weights, t_bf16, from_cache = [], None, 0
+    if all(os.path.exists(pth) for pth in paths):
+        try:
+            loaded = [layer_file.load_layer(pth, device=dev) for pth in paths]
+            t_bf16 = loaded[0].t_bf16
+            weights = [(l.wq, l.ws) for l in loaded]
+            from_cache = copies
+        except (ValueError, RuntimeError, OSError):
+            weights = []
+    if not weights:
+        x_cal = synth.draw_activations(synth.CALIB_ROWS, K_DIM, outliers, gen).float()
+        w0 = (0.02 * torch.randn(4096, K_DIM, generator=torch.Generator(device=dev).manual_seed(99), device=dev)).to(torch.bfloat16)
+        t64 = wt.solve_from_grams(wt.diag_block_gram(x_cal) / synth.CALIB_ROWS, wt.diag_block_gram(w0) / 4096)
+        t_bf16 = t64.to(torch.bfloat16).contiguous()
+        for c in range(copies):
+            wq_parts, ws_parts = [], []
+            for r0 in range(0, n_local, 8192):
+                w = (0.02 * torch.randn(min(8192, n_local - r0), K_DIM, generator=gen, device=dev)).to(torch.bfloat16)
+                q, s_ = _C.quant_int4(wt.transform_weights(w, t64).to(torch.bfloat16).contiguous())
+                wq_parts.append(q)
+                ws_parts.append(s_)
+            weights.append((torch.cat(wq_parts).contiguous(), torch.cat(ws_parts).contiguous()))
+            try:
+                layer_file.save_layer(paths[c], weights[-1][0], weights[-1][1], t_bf16, meta={"seed": 1234 + rank, "copy": c})
+            except OSError:
+                pass                                                   # no room in the temporary directory: keep going uncached
     x = synth.draw_activations(M, K_DIM, outliers, gen)
 
     def make_step(wq, ws):
@@ -234,9 +367,18 @@ def run_gpu_arm(args):
     alg_bytes = algorithmic_bytes_product(M, n_local, K_DIM)
     peak, peak_kind = measured_hbm_peak()
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": (PRODUCT_KERNEL_DRAM_BYTES * n_local // N_DIM) if M == 1 else None, "peak_kind": f"of {peak_kind}", "kernel": "w4a4 product",
-                "kernel_us": kernel_ms * 1e3, "algorithmic_bytes": alg_bytes}
+    if M <= 32:
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": (PRODUCT_KERNEL_DRAM_BYTES * n_local // N_DIM) if M == 1 else None,
+                    "traffic_source": PRODUCT_KERNEL_DRAM_SOURCE if M == 1 else None,
+                    "peak_kind": f"of {peak_kind} (a read+write copy; this kernel only reads, so a little above 1.0 is possible)",
+                    "kernel": "w4a4 product", "kernel_us": kernel_ms * 1e3, "algorithmic_bytes": alg_bytes}
+    else:                                                              # --rows beyond the decode range: the tensor cores bound it
+        tpeak, tkind = measured_peak("bf16_tflops", 1590.0)
+        tflops = 2.0 * M * n_local * K_DIM / (kernel_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": tflops, "peak": tpeak, "unit": "TFLOP/s", "frac": tflops / tpeak,
+                    "traffic": None, "peak_kind": f"of {tkind} (cuBLAS bf16; the product runs tcgen05 kind::f16)",
+                    "frac_of_nominal_int8": tflops / INT8_NOMINAL_TOPS, "kernel": "w4a4 product", "kernel_us": kernel_ms * 1e3}
 
     # ---- end to end through the public ops: host activations in, host result out -------------
     x_host = [synth.draw_activations(M, K_DIM, outliers, gen).cpu().pin_memory() for _ in range(4)]
@@ -282,6 +424,17 @@ def run_gpu_arm(args):
            "d2h_bytes_per_step": 2 * M * N_DIM, "us_per_step": 1e3 * e2e_ms / args.steps,
            "form": "CUDA Graph of pinned H2D copy -> transform+quant -> product -> pinned D2H copy"}
 
+    # ---- the other half of the metric in the same run: M = 4096 through the same layer --------
+    prefill = None
+    if not args.no_prefill:
+        prefill = measure_prefill(weights, t_bf16, outliers, gen, dev, world, n_local, barrier)
+
+    # ---- tensor-parallel FFN block with its exchange (N > 1) -----------------------------------
+    ffn_block = None
+    if world > 1 and not args.no_ffn:
+        del graphs, prod_graphs, e2e_graphs
+        ffn_block = measure_ffn_block(world, rank, dev)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -305,15 +458,16 @@ def run_gpu_arm(args):
         "metric": "w4a4_layer_eff_tops", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4", "data": "synthetic",
-        "config": {"workload": f"llama70b_gate_up_decode K={K_DIM} N={N_DIM} M={M}", "K": K_DIM, "N": N_DIM, "M": M,
-                   "sharding": f"column parallel, {n_local} columns per GPU" if world > 1 else "single GPU",
-                   "l2": f"{copies} rotating copies of the weight shard ({shard_bytes >> 20} MiB each), together > 2x L2",
-                   "timing": "CUDA Graph replay of transform+quant -> product, CUDA events, max over ranks"},
+        "config": workload_config(M),
+        "setup": {"sharding": f"column parallel, {n_local} columns per GPU" if world > 1 else "single GPU",
+                  "l2": f"{copies} rotating copies of the weight shard ({shard_bytes >> 20} MiB each), together > 2x L2",
+                  "timing": "CUDA Graph replay of transform+quant -> product, CUDA events, max over ranks",
+                  "layer_files": f"{from_cache} of {copies} weight copies loaded from {cache_dir}"},
         "us_per_layer": ms_per_step * 1e3,
         "layer_hbm_frac": algorithmic_bytes_layer(M, n_local, K_DIM) / (ms_per_step * 1e-3) / 1e9 / peak,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-        "e2e_check": e2e_check,
+        "e2e_check": e2e_check, "prefill": prefill, "ffn_block": ffn_block,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -328,6 +482,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--rows", type=int, default=1, help="activation rows M per step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the M=4096 sub-record")
+    ap.add_argument("--no-ffn", action="store_true", help="skip the FFN-block sub-record (N > 1)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 20

@@ -58,9 +58,13 @@ const char* wush_last_error(void);
  * current device is not compute capability 10.x. */
 int wush_init(void);
 
-/* Kernels that wait on barriers give up after a bounded number of polls and record that in a
- * library-owned device word instead of hanging.  This call (synchronous: it copies four bytes
- * from the device) returns the word in *flag and clears it; 0 means no kernel gave up. */
+/* Kernels that wait on barriers give up after a bounded number of polls and record that
+ * instead of hanging.  Kernels that are handed scratch by the caller (wush_w4a4_gemm with the TILE
+ * variants, wush_w4a4_gemm_tensor_scale_ws) use word 0 of that scratch.  The kernels without caller
+ * scratch use library-owned device words, which this call (synchronous: it copies a few bytes from
+ * the device) returns in *flag and clears: bits 0-7 the role code left by a streaming (DECODE)
+ * kernel, bits 8-15 the role code left by a kernel of wush_w4a4_gemm_static_scratch.
+ * 0 means no such kernel gave up since the last call. */
 int wush_device_flag(int* flag);
 
 /* --- a1: sigma-clip G=32 INT4 quantisation --------------------------------------
@@ -111,7 +115,13 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  *                        output tiles fp32 partial results of a split of K)
  * K % 32 == 0.  Ask wush_w4a4_gemm_workspace_bytes() with the SAME variant for the scratch
  * size; `workspace` may be NULL when it returns 0.  Word 0 of the scratch is an error word:
- * non-zero after the call completes means a bounded wait inside the kernel gave up. */
+ * non-zero after the call completes means a bounded wait inside the kernel gave up.
+ * Alignment: xq, wq, y and the scratch on 16 bytes; the scales on 2 bytes, and `ws` should be on
+ * 16 bytes too: up to 2048 rows TILE_F16 reads the weight scales as 16-byte vectors while it widens
+ * the weights inside the GEMM.  With a `ws` that is not, it takes the route with an fp16 copy of
+ * the weights instead, which needs 2*N*K more bytes of scratch (rounded up to 256) than
+ * wush_w4a4_gemm_workspace_bytes() reports; a scratch without that room is refused with
+ * WUSH_ERR_WORKSPACE before anything is launched. */
 typedef enum {
     WUSH_GEMM_AUTO = 0,
     WUSH_GEMM_GEMV = 1,
@@ -131,12 +141,17 @@ int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const v
  * For hosts that cannot hand this library any scratch and may not allocate device memory
  * themselves once they are running: servers that size a single arena at start-up and forbid
  * cudaMalloc afterwards, processes held to a fixed device-memory budget, control loops that
- * cannot tolerate the implicit synchronisation of an allocation.  Same result as
- * wush_w4a4_gemm(..., WUSH_GEMM_TILE_F16, ...), but the scratch is an array of
- * WUSH_STATIC_SCRATCH_BYTES that is part of the library image: every GPU that loads the library
- * keeps it until the process exits, so the limit is deliberately modest.
- *   - Shapes whose scratch (about 2*M*K bytes up to 2048 rows, 2*(M+N)*K beyond) exceeds the limit are refused with
- *     WUSH_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
+ * cannot tolerate the implicit synchronisation of an allocation.  Same arithmetic as
+ * wush_w4a4_gemm(..., WUSH_GEMM_TILE_F16, ...) (bit-identical to it wherever that call does not
+ * split K over several work units, i.e. on all but narrow layers; within the same 1e-3 of the
+ * fp64 result everywhere), but the scratch is an array of WUSH_STATIC_SCRATCH_BYTES that is part
+ * of the library image: every GPU that loads the library keeps it until the process exits, so
+ * the limit is deliberately modest.
+ *   - Scratch needed: about 2*M*K bytes when the weights are widened inside the GEMM (M <= 2048,
+ *     K % 256 == 0 and `ws` 16-byte aligned), about 2*(M+N)*K otherwise.  Shapes beyond the limit
+ *     are refused with WUSH_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
+ *   - A bounded wait that gives up inside one of its kernels shows in bits 8-15 of
+ *     wush_device_flag().
  *   - Neither this call nor anything it uses calls cudaMalloc / cudaFree or an allocating
  *     library routine.
  *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress

@@ -107,17 +107,29 @@ def measure_layer(layers: list, M: int, dev) -> dict:
     return line
 
 
-def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None) -> dict:
-    from . import _C, synth, timing
+def build_ffn_layers(tp: int, rank: int, dev, copies: int) -> list:
+    """``copies`` independently drawn (gate+up, down) shard pairs of rank ``rank`` of ``tp``: rotating
+    copies, so consecutive steps stream different weights."""
+    from . import _C, synth
+    from .linear import shard_bounds
+
+    hidden, inter = 8192, 28672
+    i0, i1 = shard_bounds(inter, tp, rank, 32)
+    il = i1 - i0
+    return [(synth.make_layer(hidden, 2 * il, seed=100 + 10 * c + rank, device=str(dev), quantiser=_C.quant_int4),
+             synth.make_layer(il, hidden, seed=200 + 10 * c + rank, device=str(dev), quantiser=_C.quant_int4))
+            for c in range(copies)]
+
+
+def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None, layers=None) -> dict:
+    from . import synth, timing
     from .linear import TensorParallelFFN, shard_bounds
 
     hidden, inter = 8192, 28672
     i0, i1 = shard_bounds(inter, tp, rank, 32)
     il = i1 - i0
     blocks = []
-    for c in range(3 if tp > 1 else 2):        # rotating copies: consecutive steps stream different weights
-        gu = synth.make_layer(hidden, 2 * il, seed=100 + 10 * c + rank, device=str(dev), quantiser=_C.quant_int4)
-        dn = synth.make_layer(il, hidden, seed=200 + 10 * c + rank, device=str(dev), quantiser=_C.quant_int4)
+    for gu, dn in (layers if layers is not None else build_ffn_layers(tp, rank, dev, 3 if tp > 1 else 2)):
         ffn = TensorParallelFFN.from_local_shards((gu.t_bf16, gu.wq, gu.ws), (dn.t_bf16, dn.wq, dn.ws), tp, rank)
         ffn.down.reduce_output = distributed
         if peer is not None:

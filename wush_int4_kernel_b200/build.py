@@ -52,15 +52,32 @@ def nvcc_path() -> str:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
+    """One object per ``.cu`` (kept under ``csrc/build/``, rebuilt only when its source or a shared
+    header changed), then one link.  No translation unit refers to another's device symbols, so
+    no relocatable device code is needed."""
+    from concurrent.futures import ThreadPoolExecutor
+
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    deps = sources + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(PKG, "..", "include", "wush_int4.h")]
-    if not force and _newer(LIB, deps):
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(PKG, "..", "include", "wush_int4.h")]
+    if not force and _newer(LIB, sources + headers):
         return LIB
-    cmd = [nvcc_path(), *NVCC_FLAGS, "-shared", "-o", LIB, *sources]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    _run(cmd)
+    objdir = os.path.join(CSRC, "build")
+    os.makedirs(objdir, exist_ok=True)
+    nvcc = nvcc_path()
+    flags = [f for f in NVCC_FLAGS if f not in ("--threads", "4")]
+    jobs = []
+    objects = []
+    for src in sources:
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        objects.append(obj)
+        if force or not _newer(obj, [src] + headers):
+            cmd = [nvcc, *flags, "-c", src, "-o", obj]
+            if verbose:
+                cmd[1:1] = ["-Xptxas", "-v"]
+            jobs.append(cmd)
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
+        list(pool.map(_run, jobs))
+    _run([nvcc, *flags, "-shared", "-o", LIB, *objects])
     return LIB
 
 

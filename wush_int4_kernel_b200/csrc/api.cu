@@ -92,7 +92,7 @@ bool f16_supported(int64_t M, int64_t N, int64_t K);
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int f16_fused_split(int64_t M, int64_t N, int64_t K);
 int f16_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
-                 size_t, cudaStream_t);
+                 size_t, cudaStream_t, int* sticky_err);
 
 // Which kernel a shape runs on.  GEMV: CUDA cores, M <= 4 (the exact per-group scaling costs
 // three instructions per (m, n, group), so beyond a few rows the dot products must move to
@@ -183,7 +183,7 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
             if (f16_supported(M, N, K)) {
                 if (!workspace) return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, none given",
                                             f16_workspace_bytes(M, N, K));
-                return f16_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
+                return f16_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st, nullptr);
             }
             // fall through: shapes the fp16 route does not take run on the exact tile kernel
         case WUSH_GEMM_TILE:

@@ -817,12 +817,22 @@ int f16_fused_split(int64_t M, int64_t N, int64_t K)
 
 // scratch: error word | fp16 activations (M x K) | [fp16 weights (N x K), unless widened in-kernel] |
 // 2^e per row of each | 2^-e per weight row | [fp32 partial results of the K ranges]
-// The _min form leaves the partial results out: with that much the product runs without the K split.
-size_t f16_workspace_bytes_min(int64_t M, int64_t N, int64_t K)
+// `fused` = the weights are widened inside the GEMM (no fp16 copy of W).  The route is decided ONCE per
+// call (f16_takes_fused) and the scratch is checked against the layout of that route.
+static size_t f16_layout_bytes(int64_t M, int64_t N, int64_t K, bool fused)
 {
-    const size_t w16 = use_fused(M, N, K) ? 0 : align256((size_t)N * K * 2);
+    const size_t w16 = fused ? 0 : align256((size_t)N * K * 2);
     return 256 + align256((size_t)M * K * 2) + w16 + align256((size_t)M * 4) + 2 * align256((size_t)N * 4);
 }
+
+// The in-kernel widening reads the weight scales as 16-byte vectors: besides the shape it needs `ws` on a
+// 16-byte boundary.  A caller whose scale pointer is only 2-byte aligned gets the pre-widened route and
+// must bring the scratch for it.
+static bool f16_takes_fused(int64_t M, int64_t N, int64_t K, const void* ws) { return use_fused(M, N, K) && aligned16(ws); }
+
+// The _min form leaves the partial results out: with that much the product runs without the K split
+// (for a 16-byte-aligned `ws`, which is what wush_w4a4_gemm_workspace_bytes assumes).
+size_t f16_workspace_bytes_min(int64_t M, int64_t N, int64_t K) { return f16_layout_bytes(M, N, K, use_fused(M, N, K)); }
 
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
@@ -831,10 +841,10 @@ size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 }
 
 static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N,
-                              int64_t K, void* y, void* workspace, size_t workspace_bytes, cudaStream_t st)
+                              int64_t K, void* y, void* workspace, size_t workspace_bytes, cudaStream_t st, int* sticky_err)
 {
     uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
-    int* err = reinterpret_cast<int*>(base);
+    int* err = sticky_err ? sticky_err : reinterpret_cast<int*>(base);
     __half* a16 = reinterpret_cast<__half*>(base + 256);
     float* fa = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + align256((size_t)M * K * 2));
     float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
@@ -842,8 +852,10 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dn) + align256((size_t)N * 4));
     int split = f16_fused_split(M, N, K);
     if (workspace_bytes < f16_workspace_bytes(M, N, K) || !aligned16(y)) split = 1;   // scratch without room for the partial results
-    cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
-    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    if (!sticky_err) {
+        cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
+        if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    }
     dequant_f16_kernel<true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
     row_shift_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)ws, fb, dn, (long long)N, (int)(K / 32));
     if (int s = check_launch("f16 pre-pass")) return s;
@@ -873,24 +885,34 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     return check_launch("gemm_f16_fused");
 }
 
+// `sticky_err`: where the kernels record a bounded wait that gave up.  Null = word 0 of the scratch, cleared
+// at the start of every call; otherwise a word the caller owns, which is only ever set (never cleared here).
 int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
-                 void* y, void* workspace, size_t workspace_bytes, cudaStream_t st)
+                 void* y, void* workspace, size_t workspace_bytes, cudaStream_t st, int* sticky_err)
 {
     if (!aligned16(y) || !aligned16(workspace))
         return fail(WUSH_ERR_INVALID_ARGUMENT, "w4a4_gemm(f16): output and workspace must be 16-byte aligned");
-    if (workspace_bytes < f16_workspace_bytes_min(M, N, K))
-        return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, %zu given",
-                    f16_workspace_bytes_min(M, N, K), workspace_bytes);
-    if (use_fused(M, N, K) && aligned16(ws))
-        return f16_fused_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
+    if ((reinterpret_cast<uintptr_t>(xs) | reinterpret_cast<uintptr_t>(ws)) & 1u)
+        return fail(WUSH_ERR_INVALID_ARGUMENT, "w4a4_gemm(f16): the bf16 scales must be 2-byte aligned");
+    const bool fused = f16_takes_fused(M, N, K, ws);                  // decided once; sizes the scratch below
+    const size_t need = f16_layout_bytes(M, N, K, fused);
+    if (workspace_bytes < need)
+        return fail(WUSH_ERR_WORKSPACE,
+                    "w4a4_gemm(f16): workspace of %zu bytes needed, %zu given%s", need, workspace_bytes,
+                    (!fused && use_fused(M, N, K))
+                        ? " (the weight scales are not 16-byte aligned, so the route with an fp16 copy of the weights is taken)"
+                        : "");
+    if (fused) return f16_fused_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st, sticky_err);
     uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
-    int* err = reinterpret_cast<int*>(base);
+    int* err = sticky_err ? sticky_err : reinterpret_cast<int*>(base);
     __half* a16 = reinterpret_cast<__half*>(base + 256);
     __half* b16 = reinterpret_cast<__half*>(base + 256 + align256((size_t)M * K * 2));
     float* fa = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(b16) + align256((size_t)N * K * 2));
     float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
-    cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
-    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    if (!sticky_err) {
+        cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
+        if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    }
     dequant_f16_kernel<false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
     dequant_f16_kernel<false><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
     if (int s = check_launch("dequant_f16")) return s;
@@ -992,12 +1014,16 @@ namespace wush {
 namespace {
 
 __device__ __align__(256) uint8_t g_static_scratch[WUSH_STATIC_SCRATCH_BYTES];
+// Where this entry point's kernels record a bounded wait that gave up.  It is only ever set by them and
+// cleared by wush_device_flag(), so a give-up is not lost when the next call starts.
+__device__ int g_static_error;
 
 constexpr int STATIC_MAX_DEVICES = 64;
 void* g_static_ptr[STATIC_MAX_DEVICES];          // device address of the array, per device (null = not resolved yet)
+int* g_static_err_ptr[STATIC_MAX_DEVICES];       // device address of g_static_error, per device
 std::mutex g_static_mutex;
 
-int static_scratch_pointer(void** out)
+int static_scratch_pointer(void** out, int** err_out)
 {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -1005,17 +1031,41 @@ int static_scratch_pointer(void** out)
     if (dev < 0 || dev >= STATIC_MAX_DEVICES) return fail(WUSH_ERR_UNSUPPORTED, "device index %d out of range", dev);
     std::lock_guard<std::mutex> lock(g_static_mutex);
     if (!g_static_ptr[dev]) {
-        void* p = nullptr;
+        void *p = nullptr, *pe = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);          // resolves the array on the CURRENT device
-        if (e != cudaSuccess || !p)
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&pe, g_static_error);
+        if (e != cudaSuccess || !p || !pe)
             return fail(WUSH_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        g_static_err_ptr[dev] = static_cast<int*>(pe);
         g_static_ptr[dev] = p;
     }
     *out = g_static_ptr[dev];
+    *err_out = g_static_err_ptr[dev];
     return WUSH_OK;
 }
 
 }  // namespace
+
+// Used by wush_device_flag(): the role code a kernel of the static-scratch entry point left on the current
+// device (0 = none, also when the entry point was never used there); clears it.  Synchronous.
+int static_scratch_take_error(int* word)
+{
+    *word = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STATIC_MAX_DEVICES) return WUSH_OK;
+    int* p;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        p = g_static_err_ptr[dev];
+    }
+    if (!p) return WUSH_OK;
+    const int zero = 0;
+    cudaError_t e = cudaMemcpy(word, p, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && *word) e = cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "device_flag(static scratch): %s", cudaGetErrorString(e));
+    return WUSH_OK;
+}
+
 }  // namespace wush
 
 WUSH_API size_t wush_w4a4_gemm_static_scratch_limit(void) { return WUSH_STATIC_SCRATCH_BYTES; }
@@ -1032,16 +1082,19 @@ WUSH_API int wush_w4a4_gemm_static_scratch(const uint8_t* xq, const void* xs, co
     if (!f16_supported(M, N, K))
         return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm_static_scratch: needs K %% 64 == 0 and N %% 8 == 0 (got K=%lld, N=%lld)",
                     (long long)K, (long long)N);
-    const size_t need = f16_workspace_bytes_min(M, N, K);
+    const size_t need = f16_layout_bytes(M, N, K, f16_takes_fused(M, N, K, ws));
     if (need > (size_t)WUSH_STATIC_SCRATCH_BYTES)
         return fail(WUSH_ERR_WORKSPACE,
                     "w4a4_gemm_static_scratch: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in array holds %zu; "
                     "use wush_w4a4_gemm with caller-provided scratch",
                     (long long)M, (long long)N, (long long)K, need, (size_t)WUSH_STATIC_SCRATCH_BYTES);
     void* scratch = nullptr;
-    if (int e = static_scratch_pointer(&scratch)) return e;
-    // f16_dispatch zeroes the error word at the head of the scratch on the stream; every other
-    // byte it reads is written first by its own pre-pass, so stale contents of an earlier call
-    // are never consumed.
-    return f16_dispatch(xq, xs, wq, ws, M, N, K, y, scratch, (size_t)WUSH_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+    int* err = nullptr;
+    if (int e = static_scratch_pointer(&scratch, &err)) return e;
+    // Every byte of the array the kernels read is written first by this call's own pre-pass, so stale
+    // contents of an earlier call are never consumed.  A bounded wait that gives up is recorded in a
+    // library-owned word that wush_device_flag() returns (and clears).  f16_dispatch checks the array's
+    // size against the route it really takes (a scale pointer that is not 16-byte aligned needs room for
+    // an fp16 copy of the weights) before anything is launched.
+    return f16_dispatch(xq, xs, wq, ws, M, N, K, y, scratch, (size_t)WUSH_STATIC_SCRATCH_BYTES, (cudaStream_t)stream, err);
 }

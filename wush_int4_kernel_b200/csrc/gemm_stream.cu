@@ -333,6 +333,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
             for (int mt = 0; mt < MT; ++mt)
                 red[(warp * MT + mt) * 32 + lane] = make_float4(acc[mt][0].x, acc[mt][0].y, acc[mt][1].x, acc[mt][1].y);
         }
+        __syncwarp();                                         // the producer's lane 0 left its loop later than lanes 1-31
         cluster.sync();
         if (warp < warps && crank == 0) {
             for (int r = 1; r < csize; ++r) {
@@ -344,6 +345,7 @@ w4a4_stream_kernel(const __grid_constant__ CUtensorMap map_wq, const __grid_cons
                 }
             }
         }
+        __syncwarp();
         cluster.sync();                                       // the partials are read: the other CTAs may leave
         if (crank != 0) return;
     }
@@ -519,14 +521,20 @@ int stream_partials(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N, 
 
 }  // namespace wush
 
+namespace wush { int static_scratch_take_error(int* word); }
+
+// Bits 0-7: role code of a streaming (decode) kernel whose wait ran out; bits 8-15: role code left by a
+// kernel of wush_w4a4_gemm_static_scratch (whose scratch, unlike a caller's, cannot be inspected from outside).
 WUSH_API int wush_device_flag(int* flag)
 {
     using namespace wush;
     if (int e = ensure_init()) return e;
     WUSH_REQUIRE(flag, "device_flag: null pointer");
-    int zero = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(flag, g_device_flag, sizeof(int));
+    int zero = 0, stream_word = 0, static_word = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&stream_word, g_device_flag, sizeof(int));
     if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_device_flag, &zero, sizeof(int));
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "device_flag: %s", cudaGetErrorString(e));
+    if (int s = static_scratch_take_error(&static_word)) return s;
+    *flag = (stream_word & 0xff) | ((static_word & 0xff) << 8);
     return WUSH_OK;
 }

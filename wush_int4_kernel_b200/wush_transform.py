@@ -38,12 +38,18 @@ def hadamard(n: int, dtype=torch.float64, device=None) -> torch.Tensor:
     return h / (n ** 0.5)
 
 
-def diag_block_gram(x: torch.Tensor, size: int = 32, dtype=torch.float64) -> torch.Tensor:
-    """(rows, K) -> (K/size, size, size): the diagonal blocks of x^T x."""
+def diag_block_gram(x: torch.Tensor, size: int = 32, dtype=torch.float64, rows_per_block: int = 8192) -> torch.Tensor:
+    """(rows, K) -> (K/size, size, size): the diagonal blocks of x^T x, accumulated over row blocks so
+    that only ``rows_per_block`` rows are ever widened to ``dtype`` at once (a 70B-size layer in fp64
+    would be several GB otherwise)."""
     rows, K = x.shape
     assert K % size == 0
-    blocks = x.to(dtype).reshape(rows, K // size, size).permute(1, 0, 2)      # (C, rows, size)
-    return blocks.transpose(1, 2) @ blocks
+    gram = torch.zeros(K // size, size, size, dtype=dtype, device=x.device)
+    for r0 in range(0, rows, rows_per_block):
+        part = x[r0:r0 + rows_per_block]
+        blocks = part.to(dtype).reshape(part.shape[0], K // size, size).permute(1, 0, 2)      # (C, rows, size)
+        gram += blocks.transpose(1, 2) @ blocks
+    return gram
 
 
 def _chol(gram: torch.Tensor) -> torch.Tensor:
