@@ -97,7 +97,7 @@ def test_device_pipeline_equals_cpu_pipeline(tmp_path):
     dev = torch.device("cuda:0")
     wq_d, ws_d, t_d, t64_d = layer_file.prepare_layer(W.to(dev), x_cal.to(dev), quantiser=_C.quant_int4, rows_per_block=128)
     rel = ((t64_d.cpu() - t64).norm() / t64.norm()).item()
-    assert rel < 1e-9, rel
+    assert rel < 1e-6, rel                   # two SVD back ends; the vectors' signs are canonical
     assert (t_d.cpu().view(torch.int16) != t.view(torch.int16)).float().mean().item() < 1e-3   # bf16 roundings of T that flip
     q, s = _C.quant_int4(wt.transform_weights(W.to(dev), t64.to(dev)).to(torch.bfloat16).contiguous())
     w_cpu = wt.transform_weights(W, t64).to(torch.bfloat16)

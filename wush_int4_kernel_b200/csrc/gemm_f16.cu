@@ -781,9 +781,22 @@ splitk_reduce_kernel(const float4* __restrict__ part, uint4* __restrict__ y, lon
 
 }  // namespace
 
+int pair_set_attributes();
+int pair_launch(bool i8, const void* a, const void* b, const float* fa, const float* fb, float alpha, const float* alpha_dev,
+                void* y, int64_t M, int64_t N, int64_t K, int* err, cudaStream_t st);
+
+// Diagnostic switch (environment, read per call): WUSH_TILE_SINGLE_CTA=1 keeps the pre-widened routes on the
+// single-CTA 256 x 256 tile kernel instead of the CTA-pair kernel, for A/B measurements of the two.
+static bool single_cta_tiles()
+{
+    const char* v = std::getenv("WUSH_TILE_SINGLE_CTA");
+    return v && v[0] == '1';
+}
+
 int f16_set_attributes()
 {
     if (int s = resolve_tensor_map_encoder()) return s;
+    if (int s = pair_set_attributes()) return s;
     cudaError_t e = cudaFuncSetAttribute(gemm_f16_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_TOTAL);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_fused2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_TOTAL);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tile2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_TOTAL);
@@ -916,6 +929,8 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     dequant_f16_kernel<false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
     dequant_f16_kernel<false><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
     if (int s = check_launch("dequant_f16")) return s;
+    if (!single_cta_tiles())
+        return pair_launch(false, a16, b16, fa, fb, 0.f, nullptr, y, M, N, K, err, st);
     CUtensorMap ma, mb;
     int s;
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;

@@ -76,6 +76,10 @@ def solve_from_grams(g_x: torch.Tensor, g_w: torch.Tensor, use_hadamard: bool = 
     # mean, so a dominant direction placed there would be clipped (10.9 % instead of 7.8 %
     # end-to-end error on the reference's outlier recipe); the weakest direction is harmless.
     u, s = u.flip(-1), s.flip(-1)
+    # A singular vector is defined up to its sign and LAPACK and cuSOLVER choose differently: make the
+    # component of largest magnitude positive, so that the CPU and the GPU solve give the same T.
+    pick = u.abs().argmax(dim=1, keepdim=True)                       # (C, 1, G): row of the largest entry per column
+    u = u * torch.sign(torch.gather(u, 1, pick))
     t = (s.clamp_min(1e-300) ** -0.5).unsqueeze(-1) * (u.transpose(1, 2) @ l_w.transpose(1, 2))
     if use_hadamard:
         t = hadamard(t.shape[-1], hi, t.device) @ t
