@@ -107,6 +107,13 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  *                        M; TILE_F16 beyond; the exact-sum TILE variant only on request)
  *   WUSH_GEMM_GEMV     : CUDA-core streaming kernel (M <= 4)
  *   WUSH_GEMM_DECODE   : tensor-core streaming kernel, weights as the wide operand (any M)
+ *   WUSH_GEMM_DECODE_TC: tcgen05 kind::i8 with the WEIGHTS as the 128-row operand and up to 32
+ *                        activation rows as N, exact int32 sum per group; the weight stream is dealt
+ *                        to the multiprocessors in equal runs of 8-group stages, so tiles may be
+ *                        split and their fp32 pieces pass through the scratch (about 5 MB);
+ *                        K % 256 == 0, M <= 32, scales 16-byte aligned.  Same results as DECODE to
+ *                        fp32 summation order; measured slower than DECODE on this part, so AUTO
+ *                        never picks it (kept as the exact tcgen05 reference of the decode path)
  *   WUSH_GEMM_TILE     : tcgen05 kind::i8 tile GEMM, exact int32 sum per group (any M)
  *   WUSH_GEMM_TILE_F16 : scales folded into exactly-representable fp16 operands, tcgen05
  *                        kind::f16 with fp32 accumulation over the whole K (any M; the fast
@@ -127,7 +134,8 @@ typedef enum {
     WUSH_GEMM_GEMV = 1,
     WUSH_GEMM_DECODE = 2,
     WUSH_GEMM_TILE = 3,
-    WUSH_GEMM_TILE_F16 = 4
+    WUSH_GEMM_TILE_F16 = 4,
+    WUSH_GEMM_DECODE_TC = 5
 } wush_gemm_variant;
 size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
 /* The variant WUSH_GEMM_AUTO stands for on the current device for this shape (one of the other

@@ -210,6 +210,64 @@ def test_decode_split_k_vs_fp64(dev, orc, shape):
     assert torch.equal(y, y2)                                              # fixed summation order
 
 
+DECODE_TC_SHAPES = [(1, 128, 256), (5, 264, 256), (8, 264, 8192), (16, 1000, 2048), (17, 520, 1024), (32, 1000, 8192),
+                    (32, 4096, 4096), (20, 19072, 512), (31, 776, 4096), (24, 2048, 2048), (9, 8, 256), (12, 130, 7168)]
+
+
+@pytest.mark.parametrize("shape", DECODE_TC_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_decode_tcgen05_swapped_vs_fp64(dev, orc, shape):
+    """The tcgen05 decode kernel (weights as the 128-row operand, 16 / 32 activation columns): ragged
+    activation rows and weight rows, one stage per tile up to 32, tiles split over several CTAs (narrow
+    layers: every tile is split) and unsplit ones, against the fp64 arbiter and against the streaming
+    kernel on the same operands; repeatable bit for bit (the pieces of a split tile are added in K order)."""
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=11 * M + N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    dops = _to_dev(dev, *ops)
+    y = cabi.gemm(*dops, variant=capi.GEMM_DECODE_TC)
+    _assert_close(y, y64, shape)
+    y2 = cabi.gemm(*dops, variant=capi.GEMM_DECODE_TC)
+    assert torch.equal(y, y2)
+    y_stream = cabi.gemm(*dops, variant=capi.GEMM_DECODE)
+    assert (y.float() - y_stream.float()).abs().max().item() <= 2e-3 * max(np.abs(y64).max(), 1e-30)
+
+
+def test_decode_tcgen05_exact_group_sums(dev, orc):
+    """One group per row with unit scales: the fp16 result IS the integer group sum (|P| <= 2048 is exact
+    in fp16), so the tensor-core path's per-group sums are checked exactly -- including code -8."""
+    M, N, K = 32, 256, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    xq = torch.randint(0, 256, (M, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    # only group 0 carries a non-zero scale: Y = P_0
+    xs = torch.zeros(M, K // 32, dtype=torch.bfloat16, device=dev)
+    ws = torch.zeros(N, K // 32, dtype=torch.bfloat16, device=dev)
+    for grp in range(K // 32):
+        xs.zero_(); ws.zero_()
+        xs[:, grp] = 1.0
+        ws[:, grp] = 1.0
+        y = cabi.gemm(xq, xs, wq, ws, variant=capi.GEMM_DECODE_TC)
+        P = orc.group_partials(xq.cpu().numpy(), wq.cpu().numpy())[:, :, grp]
+        assert np.array_equal(y.float().cpu().numpy(), P.astype(np.float32)), grp
+
+
+def test_decode_tcgen05_needs_scratch(dev):
+    """The explicit variant refuses to run without its scratch; AUTO (the streaming kernel here) needs none."""
+    lib = capi.load()
+    M, N, K = 8, 512, 1024
+    z = torch.zeros(N * K // 2, dtype=torch.uint8, device=dev)
+    s = torch.zeros(N * K // 32, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, N, dtype=torch.float16, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.wush_w4a4_gemm_workspace_bytes(M, N, K, capi.GEMM_DECODE_TC) > 256
+    assert lib.wush_w4a4_gemm(z.data_ptr(), s.data_ptr(), z.data_ptr(), s.data_ptr(), M, N, K, y.data_ptr(),
+                              capi.GEMM_DECODE_TC, None, 0, st) == capi.WUSH_ERR_WORKSPACE
+    assert lib.wush_w4a4_gemm(z.data_ptr(), s.data_ptr(), z.data_ptr(), s.data_ptr(), M, N, K, y.data_ptr(),
+                              capi.GEMM_AUTO, None, 0, st) == capi.WUSH_OK
+    torch.cuda.synchronize()
+    assert (y == 0).all()
+
+
 def test_auto_variant_by_shape(dev):
     """What AUTO stands for: the GEMV for one or two rows, the streaming kernel for decode batches and for
     mid-size M on narrow layers, the fp16 route where its tiles (or K ranges) fill the machine."""

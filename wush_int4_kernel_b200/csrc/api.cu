@@ -39,6 +39,7 @@ int mma_set_attributes();
 int tc_set_attributes();
 int stream_set_attributes();
 int f16_set_attributes();
+int decode_tc_set_attributes();
 
 static int init_device(int dev)
 {
@@ -54,6 +55,7 @@ static int init_device(int dev)
     if (int s = tc_set_attributes()) return s;
     if (int s = stream_set_attributes()) return s;
     if (int s = f16_set_attributes()) return s;
+    if (int s = decode_tc_set_attributes()) return s;
     return WUSH_OK;
 }
 
@@ -88,6 +90,10 @@ bool tc_supported(int64_t M, int64_t N, int64_t K);
 size_t tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int tc_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
                 size_t, cudaStream_t);
+bool decode_tc_supported(int64_t M, int64_t N, int64_t K);
+size_t decode_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int decode_tc_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
+                       size_t, cudaStream_t);
 bool f16_supported(int64_t M, int64_t N, int64_t K);
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int f16_fused_split(int64_t M, int64_t N, int64_t K);
@@ -109,6 +115,9 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
     // three or four rows: the tensor-core streaming kernel wins on wide layers, the CUDA-core GEMV on narrow
     // ones (a CTA of the streaming kernel is left with one or two warps there)
     if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0 || N <= 16384)) return WUSH_GEMM_GEMV;
+    // Up to 32 rows: the streaming kernel.  The tcgen05 kernel with swapped operands (DECODE_TC) computes the same
+    // product but is slower on every shape measured so far (K = 8192, N = 57344: 93 / 96 / 139 us against 55 / 77 /
+    // 119 us at M = 8 / 16 / 32), so AUTO never picks it.
     if (M <= 32) return WUSH_GEMM_DECODE;
     const bool f16_ok = f16_supported(M, N, K), stream_ok = K % 256 == 0;
     if (f16_ok && stream_ok && M <= 512) {
@@ -147,6 +156,7 @@ WUSH_API size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, 
     using namespace wush;
     if (M <= 0 || N <= 0 || K <= 0 || K % 32) return 0;
     int v = resolve_variant(variant, M, N, K);
+    if (v == WUSH_GEMM_DECODE_TC) return decode_tc_supported(M, N, K) ? decode_tc_workspace_bytes(M, N, K) : 0;
     if (v == WUSH_GEMM_TILE_F16 && f16_supported(M, N, K)) return f16_workspace_bytes(M, N, K);
     if ((v == WUSH_GEMM_TILE || v == WUSH_GEMM_TILE_F16) && tc_supported(M, N, K)) return tc_workspace_bytes(M, N, K);
     return 0;
@@ -164,7 +174,7 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
     using namespace wush;
     if (int e = ensure_init()) return e;
     WUSH_REQUIRE(M >= 0 && N >= 0 && K > 0 && K % 32 == 0, "w4a4_gemm: K must be a positive multiple of 32");
-    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_TILE_F16, "w4a4_gemm: unknown variant %d", variant);
+    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_DECODE_TC, "w4a4_gemm: unknown variant %d", variant);
     if (M == 0 || N == 0) return WUSH_OK;
     WUSH_REQUIRE(xq && xs && wq && ws && y, "w4a4_gemm: null pointer");
     WUSH_REQUIRE(aligned16(xq) && aligned16(wq), "w4a4_gemm: packed codes must be 16-byte aligned");
@@ -179,6 +189,8 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
             return gemv_dispatch(xq, xs, wq, ws, M, N, K, y, st);
         case WUSH_GEMM_DECODE:
             return mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
+        case WUSH_GEMM_DECODE_TC:
+            return decode_tc_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
         case WUSH_GEMM_TILE_F16:
             if (f16_supported(M, N, K)) {
                 if (!workspace) return fail(WUSH_ERR_WORKSPACE, "w4a4_gemm(f16): workspace of %zu bytes needed, none given",

@@ -22,6 +22,9 @@
 //               read of an accumulator arrives on rank 0's `acc_empty`
 // Every wait is bounded; a wait that gives up records a role code in the error word and the CTA falls
 // through to the common exit (cluster barrier, then tensor memory is freed).
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tc_host.cuh"
@@ -56,12 +59,22 @@ struct PairScale {
     const float* alpha_dev;     // ... or device scalar
 };
 
-// Tiles are dealt to the pairs m-fastest: the pairs that run at the same time share a few weight tiles
-// (read once from HBM, then from L2) and sweep all activation row blocks.
+// Order of the tiles.  The pairs that run at the same time should share operands (one HBM read, then L2
+// hits), and what one wave of tiles read should still be in L2 for the next.  Tiles are therefore dealt in
+// bands of `gm` row blocks: inside a band m runs fastest, so a wave covers gm row blocks x (pairs / gm)
+// weight tiles, the band's activation rows (gm x 256 x K fp16) stay L2-resident while the band sweeps N,
+// and the weights are streamed once per band.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int gm, int& tm, int& tn) {
+    const int band = t / (gm * tiles_n), r = t - band * gm * tiles_n;
+    const int rows = min(gm, tiles_m - band * gm);                  // the last band may be shorter
+    tm = band * gm + r % rows;
+    tn = r / rows;
+}
+
 template <bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const PairScale sc,
-                 __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
+                 __half* __restrict__ y, int M, int N, int K, int gm, int* __restrict__ err)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -101,7 +114,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int issued = 0;
             bool ok = true;
             for (int t = pair; t < n_tiles && ok; t += n_pairs) {
-                const int m0 = (t % tiles_m) * 2 * PM + (int)rank * PM, n0 = (t / tiles_m) * PN + (int)rank * (PN / 2);
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, gm, tm, tn);
+                const int m0 = tm * 2 * PM + (int)rank * PM, n0 = tn * PN + (int)rank * (PN / 2);
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
                     uint8_t* st = smem + slot * P_STAGE;
@@ -164,7 +179,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t ab = 0, aphase = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs) {
-            const int m0 = (t % tiles_m) * 2 * PM + (int)rank * PM, n0 = (t / tiles_m) * PN;
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, gm, tm, tn);
+            const int m0 = tm * 2 * PM + (int)rank * PM, n0 = tn * PN;
             if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -281,10 +298,17 @@ int pair_launch(bool i8, const void* a, const void* b, const float* fa, const fl
     const int64_t tiles = ((M + 2 * PM - 1) / (2 * PM)) * ((N + PN - 1) / PN);
     const int pairs = (int)(tiles < resident ? tiles : resident);
     const PairScale sc = {fa, fb, alpha, alpha_dev};
+    // Band height: as many row blocks as keep the band's activations within about a quarter of the L2
+    // (32 MB), at least 2; WUSH_PAIR_BAND overrides it for measurements.
+    const int64_t tiles_m = (M + 2 * PM - 1) / (2 * PM);
+    const int64_t slab = 2 * PM * K * (i8 ? 1 : 2);
+    int gm = (int)std::max<int64_t>(2, std::min<int64_t>(tiles_m, (32ll << 20) / slab));
+    if (const char* v = std::getenv("WUSH_PAIR_BAND")) gm = std::max(1, atoi(v));
+    if (gm > tiles_m) gm = (int)tiles_m;
     if (i8)
-        gemm_pair_kernel<true><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
+        gemm_pair_kernel<true><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, gm, err);
     else
-        gemm_pair_kernel<false><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
+        gemm_pair_kernel<false><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, gm, err);
     return check_launch("gemm_pair");
 }
 

@@ -35,12 +35,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test.  Measured on B200 for a phase that is already complete: 16 cycles, against ~190 for the
+// potentially-suspending try_wait above -- which is what a single-thread role (MMA issuer, TMA producer) pays
+// per barrier when its inputs are ready long before it asks.  Every wait below therefore tests first.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: false after WUSH_SPIN_LIMIT unsuccessful polls (each poll itself blocks for a
 // short hardware-defined time, so the limit is a few seconds at most).
 #ifndef WUSH_SPIN_LIMIT
 #define WUSH_SPIN_LIMIT (1u << 22)
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_test_wait(bar, parity)) return true;
     for (uint32_t i = 0; i < WUSH_SPIN_LIMIT; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;

@@ -4,6 +4,7 @@ small, self-contained process to capture.
 
     python -m wush_int4_kernel_b200.prof_target gemm  M N K [reps]
     python -m wush_int4_kernel_b200.prof_target gemm_ts M N K [reps]     (per-tensor scale)
+    python -m wush_int4_kernel_b200.prof_target gemm_v VARIANT M N K [reps]   (C ABI, variant gemv|decode|decode_tc|tile|tile_f16)
     python -m wush_int4_kernel_b200.prof_target fused M K   [reps]
     python -m wush_int4_kernel_b200.prof_target quant M K   [reps]
 
@@ -41,6 +42,24 @@ def main(argv):
             fn = lambda: _C.w4a4_gemv_multi(xq, xs, wq, ws)
         else:
             fn = lambda: _C.w4a4_gemm_s4(xq, xs, wq, ws)
+        work = 2.0 * M * N * K
+    elif op == "gemm_v":
+        from . import capi
+        variant = {"gemv": capi.GEMM_GEMV, "decode": capi.GEMM_DECODE, "tile": capi.GEMM_TILE, "tile_f16": capi.GEMM_TILE_F16,
+                   "decode_tc": capi.GEMM_DECODE_TC}[argv[1]]
+        M, N, K = map(int, argv[2:5])
+        reps = int(argv[5]) if len(argv) > 5 else 5
+        xq, xs = _codes(M, K, gen, dev)
+        wq, ws = _codes(N, K, gen, dev)
+        lib = capi.load()
+        nbytes = lib.wush_w4a4_gemm_workspace_bytes(M, N, K, variant)
+        work_buf = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=dev)
+        y = torch.empty(M, N, dtype=torch.float16, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def fn():
+            capi.check(lib.wush_w4a4_gemm(xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(), M, N, K, y.data_ptr(),
+                                          variant, work_buf.data_ptr() if nbytes else None, nbytes, stream), "w4a4_gemm")
         work = 2.0 * M * N * K
     elif op == "gemm_ts":
         M, N, K = map(int, argv[1:4])
