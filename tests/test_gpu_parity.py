@@ -232,6 +232,23 @@ def test_decode_tcgen05_swapped_vs_fp64(dev, orc, shape):
     assert (y.float() - y_stream.float()).abs().max().item() <= 2e-3 * max(np.abs(y64).max(), 1e-30)
 
 
+@pytest.mark.parametrize("shape", [(2100, 264, 512), (2304, 520, 1024), (300, 1000, 320)], ids=lambda s: "x".join(map(str, s)))
+def test_pair_tile_kernel_equals_single_cta_kernel(dev, orc, shape, monkeypatch):
+    """The pre-widened fp16-folded route on CTA pairs (tcgen05 cta_group::2: each CTA holds 128 activation rows
+    and half of the weight rows of a 256 x 256 tile) against the single-CTA tile kernel: same operands, same
+    accumulation order over K, so the results must agree bit for bit -- and with the fp64 arbiter."""
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=M + N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    dops = _to_dev(dev, *ops)
+    monkeypatch.setenv("WUSH_TILE_KERNEL", "pair")
+    y_pair = cabi.gemm(*dops, variant=capi.GEMM_TILE_F16)
+    monkeypatch.setenv("WUSH_TILE_KERNEL", "single")
+    y_single = cabi.gemm(*dops, variant=capi.GEMM_TILE_F16)
+    _assert_close(y_pair, y64, shape)
+    assert torch.equal(y_pair, y_single)
+
+
 def test_decode_tcgen05_exact_group_sums(dev, orc):
     """One group per row with unit scales: the fp16 result IS the integer group sum (|P| <= 2048 is exact
     in fp16), so the tensor-core path's per-group sums are checked exactly -- including code -8."""

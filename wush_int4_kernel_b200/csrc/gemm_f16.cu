@@ -785,12 +785,20 @@ int pair_set_attributes();
 int pair_launch(bool i8, const void* a, const void* b, const float* fa, const float* fb, float alpha, const float* alpha_dev,
                 void* y, int64_t M, int64_t N, int64_t K, int* err, cudaStream_t st);
 
-// Diagnostic switch (environment, read per call): WUSH_TILE_SINGLE_CTA=1 keeps the pre-widened routes on the
-// single-CTA 256 x 256 tile kernel instead of the CTA-pair kernel, for A/B measurements of the two.
-static bool single_cta_tiles()
+// Which tile kernel the pre-widened routes run on.  Measured A/B on one B200, M = 4096, N = 57344, K = 8192, whole op
+// (us, burst of 3 calls / mean of 100 back-to-back calls under the 1 kW power cap):
+//   fp16-folded (kind::f16):  single-CTA 256 x 256 tiles 2939 / 3220     CTA pairs 3035 / 3459     (cuBLAS fp16 GEMM alone 2480 / 2730)
+//   per-tensor  (kind::i8):   single-CTA 1375 / 1464                      CTA pairs 1316 / 1403
+// The pair kernel keeps the tensor pipe busier (87 % of elapsed cycles against 71 % in ncu) but the f16 product is
+// limited by the power cap, not by shared-memory traffic, so pairs only pay where the operand bytes per MMA cycle
+// are twice as many: kind::i8.  WUSH_TILE_KERNEL=pair|single overrides the choice (read per call) for measurements.
+static bool use_pair_tiles(bool i8)
 {
-    const char* v = std::getenv("WUSH_TILE_SINGLE_CTA");
-    return v && v[0] == '1';
+    if (const char* v = std::getenv("WUSH_TILE_KERNEL")) {
+        if (v[0] == 'p') return true;
+        if (v[0] == 's') return false;
+    }
+    return i8;
 }
 
 int f16_set_attributes()
@@ -929,8 +937,7 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     dequant_f16_kernel<false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
     dequant_f16_kernel<false><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
     if (int s = check_launch("dequant_f16")) return s;
-    if (!single_cta_tiles())
-        return pair_launch(false, a16, b16, fa, fb, 0.f, nullptr, y, M, N, K, err, st);
+    if (use_pair_tiles(false)) return pair_launch(false, a16, b16, fa, fb, 0.f, nullptr, y, M, N, K, err, st);
     CUtensorMap ma, mb;
     int s;
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
@@ -999,6 +1006,7 @@ int i8_tile_dispatch(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N,
     widen_s8_kernel<<<(unsigned)std::min<long long>((va + 255) / 256, cap), 256, 0, st>>>((const uint4*)xq, (uint4*)a8, va);
     widen_s8_kernel<<<(unsigned)std::min<long long>((vb + 255) / 256, cap), 256, 0, st>>>((const uint4*)wq, (uint4*)b8, vb);
     if (int s = check_launch("widen_s8")) return s;
+    if (use_pair_tiles(true)) return pair_launch(true, a8, b8, nullptr, nullptr, alpha, alpha_dev, y, M, N, K, err, st);
     CUtensorMap ma, mb;
     int s;
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a8, K, M, 128, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
