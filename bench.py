@@ -222,7 +222,7 @@ def measure_ffn_block(world, rank, dev):
     from wush_int4_kernel_b200.peer_reduce import PeerAllReduce
 
     layers = bench_matrix.build_ffn_layers(world, rank, dev, copies=3)
-    peer = PeerAllReduce(max_elements=64 * 8192)
+    peer = PeerAllReduce(max_elements=max(64 * 8192, 32 * 57344 // world))   # 64 rows of the block's output; a 32-row block of the gate+up shard
     out = {}
     for m in (1, 32, 2048):
         with_peer = bench_matrix.measure_ffn(m, world, rank, dev, True, peer, layers=layers)
@@ -231,6 +231,14 @@ def measure_ffn_block(world, rank, dev):
                        "us_nccl": with_nccl["us_per_block"], "graph": with_peer["graph"] and with_nccl["graph"],
                        "eff_tops_whole_block": with_peer["eff_tops_whole_block"]}
         torch.cuda.empty_cache()
+    # the gate+up layer alone, column parallel, full row gathered on every rank (decode sizes)
+    gather = {}
+    for m in (1, 32):
+        with_peer = bench_matrix.measure_column_gather(m, world, rank, dev, peer, layers)
+        with_nccl = bench_matrix.measure_column_gather(m, world, rank, dev, None, layers)
+        gather[str(m)] = {"us_peer_memory": with_peer["us_per_layer"], "us_nccl": with_nccl["us_per_layer"],
+                          "gather": with_peer["gather"], "graph": with_peer["graph"] and with_nccl["graph"]}
+    out["column_gather"] = gather
     err = peer.error()
     peer.close()
     out["peer_wait_timeout"] = bool(err)

@@ -229,6 +229,15 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
  *                      local memory only.  WUSH_ERR_UNSUPPORTED for other shapes (use wush_w4a4_gemm +
  *                      wush_comm_allreduce_f16).  Same calling discipline as wush_comm_allreduce_f16, and
  *                      the two may be mixed step by step;
+ *   wush_comm_allgather_f16    all-gather of the column blocks of a column-parallel product: rank r gives a
+ *                      (rows, widths[r]) fp16 block, every rank receives the (rows, sum of widths) matrix with
+ *                      the blocks side by side in rank order.  widths: host array of `world` entries, each a
+ *                      positive multiple of 8, rows * widths[r] * 2 <= slot_bytes.  Same kernel skeleton,
+ *                      calling discipline and bounded wait as wush_comm_allreduce_f16;
+ *   wush_comm_gemv_allgather   decode product of this rank's weight shard (N = widths[rank]; shapes as for
+ *                      wush_comm_gemv_allreduce) AND the all-gather: the product's epilogue stores its block
+ *                      into its slot of every rank's buffer, the gather then copies from local memory only.
+ *                      Sums, gathers and their pushed forms may be mixed step by step;
  *   wush_comm_connect_pointer  the same for a peer buffer of THIS process (wush_comm_base of another
  *                      communicator on a device with peer access): emulation of several ranks in one
  *                      process, and tests;
@@ -245,6 +254,11 @@ int wush_comm_set_poll_limit(void* comm, unsigned int polls);
 int wush_comm_allreduce_f16(void* comm, const void* partial, void* out, int64_t n, void* stream);
 int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq,
                              const void* ws, int64_t M, int64_t N, int64_t K, void* out, void* stream);
+int wush_comm_allgather_f16(void* comm, const void* local, void* out, int64_t rows, const int64_t* widths,
+                            void* stream);
+int wush_comm_gemv_allgather(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq,
+                             const void* ws, int64_t M, int64_t K, const int64_t* widths, void* out,
+                             void* stream);
 int wush_comm_error(void* comm, int* error);
 int wush_comm_destroy(void* comm);
 

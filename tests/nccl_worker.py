@@ -68,6 +68,23 @@ def main():
         plain = peer(w4a4_product(xq_l, xs_l, shard.local.wq, shard.local.ws))
         assert torch.equal(fused, plain), f"pushed product differs at rows={rows}"
     assert peer.error() == 0
+    # all-gather of column blocks over peer memory, equal and unequal widths: the pull kernel and the product that
+    # pushes its block, against the library all-gather of the same blocks (bit for bit); several steps, mixed with sums
+    for multiple in (32, 256):
+        colp = ColumnParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, multiple=multiple, gather_output=True,
+                                        peer_gather=peer)
+        coln = ColumnParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, multiple=multiple, gather_output=True)
+        for rows in (1, 2, 8, 32, 5, 40):
+            xr = synth.draw_activations(rows, 1024, layer.outliers, gen)
+            want = coln(xr)
+            got = colp(xr)
+            assert torch.equal(got, want), f"peer all-gather differs at rows={rows}, multiple={multiple}"
+            xq_f, xs_f = quantise_activations(xr, layer.t_bf16)
+            assert torch.equal(want, w4a4_product(xq_f, xs_f, layer.wq, layer.ws)), "sharded columns differ from the unsharded product"
+            blk = w4a4_product(xq_f, xs_f, colp.local.wq, colp.local.ws)
+            assert torch.equal(peer.allgather(blk, colp.widths), want), f"pull all-gather differs at rows={rows}"
+            assert torch.equal(peer(blk), peer(blk)), "sum between gathers"
+    assert peer.error() == 0
     row2 = RowParallelW4A4Linear(layer.t_bf16, layer.wq, layer.ws, world, rank, peer_reduce=peer)
     y2 = row2(x[:, k0:k1].contiguous())
     assert ((y2.float() - full.float()).norm() / full.float().norm()).item() <= 2e-3

@@ -216,3 +216,93 @@ def test_pushed_gemv_allreduce_single_rank(setup, M, N, K):
         assert err.value == 0
     finally:
         capi.check(lib.wush_comm_destroy(comm), "comm_destroy")
+
+
+def _widths(values):
+    import ctypes
+    return (ctypes.c_int64 * len(values))(*values)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 768, 1024), (2, 1000, 4096), (8, 1000, 4096), (32, 768, 2048)])
+def test_peer_allgather_single_rank(setup, M, N, K):
+    """World of one: the gather is a copy through the slot (pull form) and the product's pushed
+    block comes back unchanged (pushed form); bad widths are refused before any launch."""
+    import ctypes
+    from tests import cabi
+    from wush_int4_kernel_b200 import capi
+    _C, synth, layer, gen = setup
+    lib = capi.load()
+    xq = torch.randint(0, 256, (M, K // 2), generator=gen, device="cuda", dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=gen, device="cuda", dtype=torch.uint8)
+    xs = (0.02 * (1 + torch.rand(M, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
+    ws = (0.01 * (1 + torch.rand(N, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
+    expect = cabi.gemm(xq, xs, wq, ws, capi.GEMM_GEMV if M <= 2 else capi.GEMM_DECODE)
+    comm = ctypes.c_void_p()
+    capi.check(lib.wush_comm_create(0, 1, 64 * 1024, ctypes.byref(comm)), "comm_create")
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        for step in range(3):
+            out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+            capi.check(lib.wush_comm_gemv_allgather(comm, xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(), M, K,
+                                                    _widths([N]), out.data_ptr(), stream), "gemv_allgather")
+            assert torch.equal(out, expect), step
+            plain = torch.zeros_like(expect)
+            capi.check(lib.wush_comm_allgather_f16(comm, expect.data_ptr(), plain.data_ptr(), M, _widths([N]), stream), "allgather")
+            assert torch.equal(plain, expect)
+        assert lib.wush_comm_allgather_f16(comm, expect.data_ptr(), plain.data_ptr(), M, _widths([N - 4]), stream) != 0   # not a multiple of 8
+        assert lib.wush_comm_allgather_f16(comm, expect.data_ptr(), plain.data_ptr(), 64, _widths([N]), stream) != 0     # larger than a slot
+        err = ctypes.c_int(-1)
+        capi.check(lib.wush_comm_error(comm, ctypes.byref(err)), "comm_error")
+        assert err.value == 0
+    finally:
+        capi.check(lib.wush_comm_destroy(comm), "comm_destroy")
+
+
+@pytest.mark.parametrize("M", [1, 2, 8, 32])
+def test_peer_allgather_two_ranks_one_after_the_other(setup, M):
+    """World of two in one process, blocks of unequal width.  The two ranks' kernels never run at
+    the same time: rank 1 goes first with a wait of ~2 ms that runs out (nobody has published for
+    rank 0 yet) -- its block and its flag are in place by then --, then rank 0 runs and finds
+    everything there.  Checks the slot / offset arithmetic of both forms against the plain products."""
+    import ctypes
+    from tests import cabi
+    from wush_int4_kernel_b200 import capi
+    _C, synth, layer, gen = setup
+    lib = capi.load()
+    K, widths = 1024, [512, 256]
+    xq = torch.randint(0, 256, (M, K // 2), generator=gen, device="cuda", dtype=torch.uint8)
+    xs = (0.02 * (1 + torch.rand(M, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
+    wq = [torch.randint(0, 256, (w, K // 2), generator=gen, device="cuda", dtype=torch.uint8) for w in widths]
+    ws = [(0.01 * (1 + torch.rand(w, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16) for w in widths]
+    blocks = [cabi.gemm(xq, xs, wq[r], ws[r], capi.GEMM_GEMV if M <= 2 else capi.GEMM_DECODE) for r in range(2)]
+    expect = torch.cat(blocks, dim=1)
+    stream = torch.cuda.current_stream().cuda_stream
+    for pushed in (False, True):
+        comms = [ctypes.c_void_p(), ctypes.c_void_p()]
+        for r in range(2):
+            capi.check(lib.wush_comm_create(r, 2, 64 * 1024, ctypes.byref(comms[r])), "comm_create")
+        try:
+            for r in range(2):
+                base = ctypes.c_void_p()
+                capi.check(lib.wush_comm_base(comms[1 - r], ctypes.byref(base)), "comm_base")
+                capi.check(lib.wush_comm_connect_pointer(comms[r], 1 - r, base), "comm_connect_pointer")
+            capi.check(lib.wush_comm_set_poll_limit(comms[1], 4096), "comm_set_poll_limit")
+            outs = [torch.zeros(M, sum(widths), dtype=torch.float16, device="cuda") for _ in range(2)]
+            for r in (1, 0):
+                if pushed:
+                    capi.check(lib.wush_comm_gemv_allgather(comms[r], xq.data_ptr(), xs.data_ptr(), wq[r].data_ptr(), ws[r].data_ptr(),
+                                                            M, K, _widths(widths), outs[r].data_ptr(), stream), "gemv_allgather")
+                else:
+                    capi.check(lib.wush_comm_allgather_f16(comms[r], blocks[r].data_ptr(), outs[r].data_ptr(), M, _widths(widths),
+                                                           stream), "allgather")
+                torch.cuda.synchronize()
+            errs = []
+            for r in range(2):
+                e = ctypes.c_int(-1)
+                capi.check(lib.wush_comm_error(comms[r], ctypes.byref(e)), "comm_error")
+                errs.append(e.value)
+            assert errs == [0, 1]                                # rank 1 gave up as planned, rank 0 saw both blocks
+            assert torch.equal(outs[0], expect), pushed
+        finally:
+            for c in comms:
+                capi.check(lib.wush_comm_destroy(c), "comm_destroy")

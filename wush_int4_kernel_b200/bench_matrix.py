@@ -165,6 +165,41 @@ def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None, l
             "weight_bytes_per_rank": wbytes, "weight_stream_gbs_per_rank": round(wbytes / t / 1e3, 1)}
 
 
+def measure_column_gather(M: int, tp: int, rank: int, dev, peer, layers) -> dict:
+    """The gate+up layer column parallel with the full row gathered on every rank (what a caller
+    outside an FFN block needs): the product pushing its block into every rank's buffer (``peer``) or
+    the library all-gather (``peer`` None).  ``layers``: the pairs of ``build_ffn_layers``."""
+    import torch.distributed as dist
+
+    from . import synth, timing
+    from .linear import ColumnParallelW4A4Linear
+
+    cols = []
+    for gu, _ in layers:
+        col = ColumnParallelW4A4Linear.__new__(ColumnParallelW4A4Linear)    # from tensors that already are this rank's shard
+        n_loc = gu.wq.shape[0]
+        col.world, col.rank, col.group, col.gather_output, col.peer_gather = tp, rank, None, True, peer
+        col.full_out, col.widths = n_loc * tp, [n_loc] * tp
+        col.bounds = [(r * n_loc, (r + 1) * n_loc) for r in range(tp)]
+        from .linear import W4A4Linear
+        col.local = W4A4Linear(gu.t_bf16, gu.wq, gu.ws)
+        cols.append(col)
+    x = synth.draw_activations(M, 8192, layers[0][0].outliers, torch.Generator(device=dev).manual_seed(9))
+    captured = True
+    try:
+        graphs = [timing.capture(lambda c=c: c(x))[0] for c in cols]
+        t = _median_us(graphs, _reps(M))
+    except RuntimeError:
+        captured = False
+        torch.cuda.synchronize()
+        t = timing.median_of(lambda: [c(x) for c in cols], max(2, _reps(M) // len(cols))) / len(cols)
+    tt = torch.tensor([t], device=dev)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    return {"M": M, "tp": tp, "us_per_layer": round(float(tt.item()), 2), "graph": captured,
+            "gather": "library all-gather" if peer is None else
+                      ("peer memory, pushed from the product kernel" if M <= 32 else "peer memory, one kernel")}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="qwen,llama,square,prefill")

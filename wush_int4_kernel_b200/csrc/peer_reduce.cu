@@ -43,9 +43,11 @@ namespace {
 constexpr int PR_THREADS = 256;
 constexpr uint32_t PR_POLL_LIMIT = 1u << 21;        // default bound of a wait: x ~0.5 us of back-off per poll
 
-__global__ void __launch_bounds__(PR_THREADS)
-peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, long long n_vec,   // 8 halves per vector
-                          const PeerTable peers, int pushed)
+// Steps 1-3 of an exchange, shared by the sum and the gather: write the contribution (unless the
+// producer kernel pushed it), publish, wait -- bounded -- until every rank has published this step.
+// Called by all threads of every CTA; returns the step number and whether the wait succeeded.
+__device__ __forceinline__ bool exchange_begin(const uint4* __restrict__ local, long long n_vec, const PeerTable& peers,
+                                               int pushed, unsigned int* step_out)
 {
     __shared__ unsigned int s_step, s_ok;
     CommState* state = peers.state;
@@ -86,9 +88,38 @@ peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ o
         }
     }
     __syncthreads();
+    *step_out = step;
+    return s_ok != 0;
+}
+
+// The last CTA out advances the step counter and clears the arrival counters.
+__device__ __forceinline__ void exchange_end(const PeerTable& peers, unsigned int step)
+{
+    CommState* state = peers.state;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int finished = atomicAdd(&state->done, 1u);
+        if (finished == gridDim.x - 1) {
+            state->copied = 0;
+            state->done = 0;
+            __threadfence();
+            state->step = step + 1u;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(PR_THREADS)
+peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, long long n_vec,   // 8 halves per vector
+                          const PeerTable peers, int pushed)
+{
+    const int rank = peers.rank, world = peers.world;
+    const long long stride = (long long)gridDim.x * PR_THREADS;
+    const long long first = (long long)blockIdx.x * PR_THREADS + threadIdx.x;
+    unsigned int step;
+    const bool ok = exchange_begin(local, n_vec, peers, pushed, &step);
 
     // 4. reduce in rank order
-    if (s_ok) {
+    if (ok) {
         for (long long i = first; i < n_vec; i += stride) {
             // all peers' vectors are requested before the first one is used: one NVLink round trip, not `world`
             uint4 v[PR_MAX_WORLD];
@@ -121,16 +152,42 @@ peer_allreduce_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ o
             out[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int finished = atomicAdd(&state->done, 1u);
-        if (finished == gridDim.x - 1) {                               // last CTA out: next step
-            state->copied = 0;
-            state->done = 0;
-            __threadfence();
-            state->step = step + 1u;
+    exchange_end(peers, step);
+}
+
+// All-gather of column blocks: rank r contributes a (rows, width[r]) fp16 block (row-major in its slot), the
+// result is the (rows, sum of widths) matrix with the blocks side by side in rank order.  Widths and offsets
+// are in 16-byte vectors (8 halves).
+struct GatherShape {
+    int width[PR_MAX_WORLD];
+    int offset[PR_MAX_WORLD];
+    int total;
+};
+
+__global__ void __launch_bounds__(PR_THREADS)
+peer_allgather_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, int rows, const GatherShape shape,
+                          const PeerTable peers, int pushed)
+{
+    const int rank = peers.rank, world = peers.world;
+    const long long stride = (long long)gridDim.x * PR_THREADS;
+    const long long first = (long long)blockIdx.x * PR_THREADS + threadIdx.x;
+    unsigned int step;
+    const bool ok = exchange_begin(local, (long long)rows * shape.width[rank], peers, pushed, &step);
+
+    // 4. copy: the output is walked in its own order (coalesced stores), the source slot found per vector
+    if (ok) {
+        const long long n_out = (long long)rows * shape.total;
+        for (long long j = first; j < n_out; j += stride) {
+            const int row = (int)(j / shape.total), c = (int)(j - (long long)row * shape.total);
+            int src = 0;
+#pragma unroll
+            for (int r = 1; r < PR_MAX_WORLD; ++r)
+                if (r < world && c >= shape.offset[r]) src = r;
+            const uint4* slot = reinterpret_cast<const uint4*>(peers.base[pushed ? rank : src] + slot_offset(peers, step, src));
+            out[j] = ld_sys_v4(slot + (long long)row * shape.width[src] + (c - shape.offset[src]));
         }
     }
+    exchange_end(peers, step);
 }
 
 struct Comm {
@@ -168,6 +225,36 @@ int launch_reduce(const Comm* c, const PeerTable& t, const void* partial, void* 
     cudaError_t e = launch_dependent(peer_allreduce_f16_kernel, dim3((unsigned)blocks), dim3(PR_THREADS), (size_t)0, st,
                                      (const uint4*)partial, (uint4*)out, n_vec, t, pushed);
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_allreduce launch: %s", cudaGetErrorString(e));
+    return WUSH_OK;
+}
+
+int gather_shape(const Comm* c, const int64_t* widths, int64_t rows, GatherShape* g, const char* what)
+{
+    if (!widths) return fail(WUSH_ERR_INVALID_ARGUMENT, "%s: null widths", what);
+    int64_t off = 0;
+    for (int r = 0; r < PR_MAX_WORLD; ++r) { g->width[r] = 0; g->offset[r] = 0; }
+    for (int r = 0; r < c->world; ++r) {
+        const int64_t w = widths[r];
+        if (w <= 0 || w % 8 != 0) return fail(WUSH_ERR_INVALID_ARGUMENT, "%s: width of rank %d (%lld) must be a positive multiple of 8", what, r, (long long)w);
+        if ((size_t)(rows * w) * 2 > c->slot_bytes)
+            return fail(WUSH_ERR_INVALID_ARGUMENT, "%s: %lld x %lld halves do not fit the slot of %zu bytes", what, (long long)rows, (long long)w, c->slot_bytes);
+        g->width[r] = (int)(w / 8);
+        g->offset[r] = (int)(off / 8);
+        off += w;
+    }
+    if (off / 8 > INT32_MAX / 2 || rows > INT32_MAX / 2) return fail(WUSH_ERR_INVALID_ARGUMENT, "%s: result too large", what);
+    g->total = (int)(off / 8);
+    return WUSH_OK;
+}
+
+int launch_gather(const Comm* c, const PeerTable& t, const void* local, void* out, int64_t rows, const GatherShape& g, int pushed,
+                  cudaStream_t st)
+{
+    long long blocks = ((long long)rows * g.total + PR_THREADS - 1) / PR_THREADS;
+    if (blocks > sm_count()) blocks = sm_count();                       // every CTA resident while it waits
+    cudaError_t e = launch_dependent(peer_allgather_f16_kernel, dim3((unsigned)blocks), dim3(PR_THREADS), (size_t)0, st,
+                                     (const uint4*)local, (uint4*)out, (int)rows, g, t, pushed);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_allgather launch: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
 
@@ -316,6 +403,51 @@ WUSH_API int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void*
                         : stream_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream))
         return s;
     return launch_reduce(c, t, nullptr, out, M * N, 1, (cudaStream_t)stream);
+}
+
+// All-gather of the column blocks of a column-parallel product: out (rows, sum of widths) receives rank r's
+// (rows, widths[r]) block at column offset widths[0] + .. + widths[r-1].
+WUSH_API int wush_comm_allgather_f16(void* comm, const void* local, void* out, int64_t rows, const int64_t* widths, void* stream)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm, "comm_allgather: null communicator");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(rows >= 0, "comm_allgather: bad row count");
+    GatherShape g;
+    if (int s = gather_shape(c, widths, rows, &g, "comm_allgather")) return s;
+    if (rows == 0) return WUSH_OK;
+    WUSH_REQUIRE(local && out && aligned16(local) && aligned16(out), "comm_allgather: pointers must be 16-byte aligned");
+    PeerTable t;
+    if (int s = fill_table(c, &t, "comm_allgather")) return s;
+    return launch_gather(c, t, local, out, rows, g, 0, (cudaStream_t)stream);
+}
+
+// Column-parallel decode product and the all-gather of its column blocks as one chain: the product's
+// epilogue stores this rank's (M, widths[rank]) block into its slot of EVERY rank's buffer, the gather
+// that follows reads only local memory.  Shapes as for wush_comm_gemv_allreduce (N = widths[rank]).
+WUSH_API int wush_comm_gemv_allgather(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws,
+                                      int64_t M, int64_t K, const int64_t* widths, void* out, void* stream)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm, "comm_gemv_allgather: null communicator");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(M >= 1 && K > 0 && K % 32 == 0, "comm_gemv_allgather: bad shape");
+    WUSH_REQUIRE(xq && xs && wq && ws && out, "comm_gemv_allgather: null pointer");
+    WUSH_REQUIRE(aligned16(xq) && aligned16(wq) && aligned16(out), "comm_gemv_allgather: pointers must be 16-byte aligned");
+    GatherShape g;
+    if (int s = gather_shape(c, widths, M, &g, "comm_gemv_allgather")) return s;
+    const int64_t N = widths[c->rank];
+    const bool by_gemv = M <= 2 && gemv_smem_bytes((int)M, K) <= 200 * 1024;
+    const bool by_stream = M <= 32 && stream_supported(K, xs, ws);
+    if (!by_gemv && !by_stream)
+        return fail(WUSH_ERR_UNSUPPORTED, "comm_gemv_allgather: M=%lld K=%lld is outside the pushed kernels' range", (long long)M,
+                    (long long)K);
+    PeerTable t;
+    if (int s = fill_table(c, &t, "comm_gemv_allgather")) return s;
+    if (int s = by_gemv ? gemv_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream)
+                        : stream_dispatch_push(xq, xs, wq, ws, M, N, K, t, (cudaStream_t)stream))
+        return s;
+    return launch_gather(c, t, nullptr, out, M, g, 1, (cudaStream_t)stream);
 }
 
 WUSH_API int wush_comm_error(void* comm, int* error)

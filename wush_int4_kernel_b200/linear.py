@@ -6,7 +6,9 @@ Sharding (none exists in the reference; the composition is pinned by the single-
 
 * column parallel -- the rows of ``wq`` / ``ws`` (= columns of Y) are split; X, T and the
   activation quantisation are replicated; no collective unless the caller asks for the full
-  row (``gather_output=True`` -> one all-gather of ``(M, N/p)`` fp16 blocks);
+  row (``gather_output=True`` -> one all-gather of ``(M, N/p)`` fp16 blocks: with a peer
+  communicator attached the decode product stores its block straight into every rank's buffer,
+  otherwise the library all-gather);
 * row parallel -- K is split on multiples of 32 so each rank keeps whole transform blocks and
   whole scale groups; every rank produces a partial ``(M, N)`` product and one all-reduce
   (sum, fp32) finishes it.
@@ -86,18 +88,31 @@ class ColumnParallelW4A4Linear:
     """Rank ``rank`` of ``world`` holds output columns ``shard_bounds(N, world, rank, multiple)``."""
 
     def __init__(self, t, wq, ws, world: int, rank: int, multiple: int = 1, gather_output: bool = False,
-                 group=None):
+                 group=None, peer_gather=None):
         self.full_out = wq.shape[0]
         self.world, self.rank, self.group, self.gather_output = world, rank, group, gather_output
+        self.peer_gather = peer_gather          # optional peer_reduce.PeerAllReduce for decode-size results
         self.n0, self.n1 = shard_bounds(self.full_out, world, rank, multiple)
         self.local = W4A4Linear(t, wq[self.n0:self.n1].contiguous(), ws[self.n0:self.n1].contiguous())
         self.bounds = [shard_bounds(self.full_out, world, r, multiple) for r in range(world)]
+        self.widths = [b - a for a, b in self.bounds]
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        y = self.local(x)
         if not self.gather_output or self.world == 1:
-            return y
-        return gather_columns(y, self.bounds, self.group)
+            return self.local(x)
+        lead = x.shape[:-1]
+        peer = self.peer_gather
+        if peer is not None:
+            # at most 32 rows: the product pushes its block into every rank's buffer and the gather is local;
+            # larger results that fit a slot: one gather kernel over peer memory
+            xq, xs = quantise_activations(x.reshape(-1, x.shape[-1]), self.local.t)
+            y = peer.product_allgather(xq, xs, self.local.wq, self.local.ws, self.widths)
+            if y is None:
+                y = w4a4_product(xq, xs, self.local.wq, self.local.ws)
+                y = peer.allgather(y, self.widths) if peer.fits_gather(y.shape[0], self.widths) else \
+                    gather_columns(y, self.bounds, self.group)
+            return y.reshape(*lead, self.full_out)
+        return gather_columns(self.local(x), self.bounds, self.group)
 
 
 def gather_columns(y_local: torch.Tensor, bounds, group=None) -> torch.Tensor:
@@ -106,6 +121,10 @@ def gather_columns(y_local: torch.Tensor, bounds, group=None) -> torch.Tensor:
 
     width = max(b - a for a, b in bounds)
     lead = y_local.shape[:-1]
+    if all(b - a == width for a, b in bounds):               # equal blocks: no padding pass
+        parts = [torch.empty_like(y_local) for _ in bounds]
+        dist.all_gather(parts, y_local.contiguous(), group=group)
+        return torch.cat(parts, dim=-1)
     padded = y_local.new_zeros(*lead, width)
     padded[..., : y_local.shape[-1]] = y_local
     parts = [torch.empty_like(padded) for _ in bounds]

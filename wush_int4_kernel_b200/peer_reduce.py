@@ -1,7 +1,8 @@
-"""One-shot all-reduce of small fp16 partial products over NVLink peer memory: the Python face of
-the ``wush_comm_*`` entry points (``csrc/peer_reduce.cu``).  The reference is single-GPU and has
-nothing like it; here it finishes the row-parallel down projection of the tensor-parallel FFN
-block at decode sizes, where a library all-reduce costs several times the sharded product.
+"""One-shot all-reduce and all-gather of small fp16 products over NVLink peer memory: the Python face
+of the ``wush_comm_*`` entry points (``csrc/peer_reduce.cu``).  The reference is single-GPU and has
+nothing like it; here the sum finishes the row-parallel down projection of the tensor-parallel FFN
+block and the gather a column-parallel layer whose caller needs the full row, at decode sizes,
+where a library collective costs several times the sharded product.
 
 One process per GPU of ONE node.  Construction is collective over ``group`` (it exchanges CUDA IPC
 handles through ``torch.distributed``); calls are one kernel launch on the current stream and
@@ -66,6 +67,42 @@ class PeerAllReduce:
         capi.check(self.lib.wush_comm_gemv_allreduce(self.comm, xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(),
                                                      rows, n, K, out.data_ptr(), torch.cuda.current_stream().cuda_stream),
                    "comm_gemv_allreduce")
+        return out
+
+    def _widths(self, widths):
+        if len(widths) != self.world:
+            raise ValueError(f"PeerAllReduce: {len(widths)} widths for a world of {self.world}")
+        return (ctypes.c_int64 * self.world)(*[int(w) for w in widths])
+
+    def fits_gather(self, rows: int, widths) -> bool:
+        return all(w > 0 and w % 8 == 0 and rows * w <= self.max_elements for w in widths)
+
+    def allgather(self, y_local: torch.Tensor, widths) -> torch.Tensor:
+        """All-gather of column blocks: ``y_local`` is this rank's contiguous ``(rows, widths[rank])``
+        fp16 block, the result the ``(rows, sum(widths))`` matrix with all ranks' blocks in rank order."""
+        rows = y_local.numel() // y_local.shape[-1]
+        if (y_local.dtype != torch.float16 or not y_local.is_cuda or not y_local.is_contiguous()
+                or y_local.shape[-1] != widths[self.rank] or not self.fits_gather(rows, widths)):
+            raise ValueError("PeerAllReduce.allgather: needs contiguous CUDA fp16 blocks whose widths are multiples of 8 and fit the slot")
+        out = torch.empty(*y_local.shape[:-1], sum(widths), dtype=torch.float16, device=y_local.device)
+        capi.check(self.lib.wush_comm_allgather_f16(self.comm, y_local.data_ptr(), out.data_ptr(), rows, self._widths(widths),
+                                                    torch.cuda.current_stream().cuda_stream), "comm_allgather_f16")
+        return out
+
+    def product_allgather(self, xq, xs, wq, ws, widths):
+        """Column-parallel decode product (at most 32 activation rows) and the all-gather of its column
+        blocks in one chain: the product kernel pushes this rank's block into every rank's buffer.
+        Returns ``None`` for shapes outside the pushed kernels' range."""
+        K = wq.shape[1] * 2
+        rows = xq.numel() // (K // 2)
+        by_gemv = rows <= 2 and rows * (K // 32) * 36 <= 200 * 1024
+        by_stream = rows <= 32 and K % 256 == 0 and xs.data_ptr() % 16 == 0 and ws.data_ptr() % 16 == 0
+        if not (by_gemv or by_stream) or wq.shape[0] != widths[self.rank] or not self.fits_gather(rows, widths):
+            return None
+        out = torch.empty(rows, sum(widths), dtype=torch.float16, device=xq.device)
+        capi.check(self.lib.wush_comm_gemv_allgather(self.comm, xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(),
+                                                     rows, K, self._widths(widths), out.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream), "comm_gemv_allgather")
         return out
 
     def error(self) -> int:
