@@ -103,30 +103,56 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One row's 8 outputs held by one lane -> statistics over the quad -> one word of codes.
-__device__ __forceinline__ void quantise_row_octet(const float (&v)[8], uint32_t* word, uint32_t* sbits) {
-    float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) { s1 += v[e]; s2 = fmaf(v[e], v[e], s2); }
-    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+// Two rows' 8 outputs each (row a = gid, row b = gid + 8) held by one lane as four float2 per row ->
+// statistics over the quad -> one word of codes per row.  Instruction count is what bounds this kernel
+// at prefill sizes, hence:
+//   * sums and sums of squares on packed fp32 pairs;
+//   * the quad reduction is a transposing butterfly: after the first exchange even lanes carry row a's
+//     (s1, s2) and odd lanes row b's, so the second exchange and the whole scale chain (square root,
+//     bf16 rounding, reciprocal) run ONCE for both rows -- lanes of either parity work on their own row --
+//     and one more exchange hands each lane the other row's reciprocal;
+//   * clamping rides the FMA: u = sat(v / (14 scale) + 1/2) is clamp((q + 7) / 14, 0, 1), a second FMA
+//     onto 1.5 * 2^23 rounds 14 u to the integer q + 7 in the low mantissa bits.  The intermediate
+//     rounding of u moves a code only where v / scale is within ~1e-6 of a tie.
+// `sbits` is row a's scale on even lanes and row b's on odd lanes.
+__device__ __forceinline__ void quantise_two_row_octets(const float2 (&a)[4], const float2 (&b)[4], int lane, uint32_t* word_a,
+                                                        uint32_t* word_b, uint32_t* sbits) {
+    float2 sa = __fadd2_rn(__fadd2_rn(a[0], a[1]), __fadd2_rn(a[2], a[3]));
+    float2 sb = __fadd2_rn(__fadd2_rn(b[0], b[1]), __fadd2_rn(b[2], b[3]));
+    float2 qa = __ffma2_rn(a[3], a[3], __ffma2_rn(a[2], a[2], __ffma2_rn(a[1], a[1], __fmul2_rn(a[0], a[0]))));
+    float2 qb = __ffma2_rn(b[3], b[3], __ffma2_rn(b[2], b[2], __ffma2_rn(b[1], b[1], __fmul2_rn(b[0], b[0]))));
+    const float2 xa = make_float2(sa.x + sa.y, qa.x + qa.y), xb = make_float2(sb.x + sb.y, qb.x + qb.y);   // (s1, s2) per row
+    const bool odd = lane & 1;
+    float2 keep = odd ? xb : xa;
+    const float2 send = odd ? xa : xb;
+    keep.x += __shfl_xor_sync(0xffffffffu, send.x, 1);
+    keep.y += __shfl_xor_sync(0xffffffffu, send.y, 1);
+    keep.x += __shfl_xor_sync(0xffffffffu, keep.x, 2);
+    keep.y += __shfl_xor_sync(0xffffffffu, keep.y, 2);
     float scale;
-    *sbits = sigma_clip_scale(s1, s2, &scale);
-    const float inv = __frcp_rn(scale);
-    const float magic = 12582912.f;                       // 1.5 * 2^23: low mantissa bits = rint()
-    // bits(f) = bits(magic) + q exactly, so sum_e bits(f_e) * 16^e (mod 2^32) is the packed word of the
-    // offset nibbles q + 8 plus a constant; one multiply-add per element, then the constant comes
-    // off and the offset is undone by flipping bit 3 of every nibble.
-    uint32_t w = 0;
+    *sbits = sigma_clip_scale(keep.x, keep.y, &scale);
+    const float mine = __frcp_rn(scale) * (1.0f / 14.0f);
+    const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+    const float inv_a = odd ? other : mine, inv_b = odd ? mine : other;
+    const float2 fourteen = make_float2(14.f, 14.f), magic = make_float2(12582912.f, 12582912.f);   // 1.5 * 2^23
+    uint32_t wa = 0, wb = 0;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        float f = fmaf(v[e], inv, magic);
-        f = fminf(fmaxf(f, magic - 7.f), magic + 7.f);
-        w = __float_as_uint(f) * (1u << (4 * e)) + w;
+    for (int e = 0; e < 4; ++e) {
+        float2 ua, ub;
+        asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(ua.x) : "f"(a[e].x), "f"(inv_a));
+        asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(ua.y) : "f"(a[e].y), "f"(inv_a));
+        asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(ub.x) : "f"(b[e].x), "f"(inv_b));
+        asm("fma.rn.sat.f32 %0, %1, %2, 0f3F000000;" : "=f"(ub.y) : "f"(b[e].y), "f"(inv_b));
+        const float2 fa = __ffma2_rn(ua, fourteen, magic), fb = __ffma2_rn(ub, fourteen, magic);
+        // bits(f) = bits(magic) + (q + 7): one multiply-add per element builds the word of nibbles q + 7 plus a constant
+        wa = __float_as_uint(fa.x) * (1u << (8 * e)) + wa;
+        wa = __float_as_uint(fa.y) * (1u << (8 * e + 4)) + wa;
+        wb = __float_as_uint(fb.x) * (1u << (8 * e)) + wb;
+        wb = __float_as_uint(fb.y) * (1u << (8 * e + 4)) + wb;
     }
-    *word = (w - (0x4B400000u - 8u) * 0x11111111u) ^ 0x88888888u;
+    // constant off with q + 8 left in every nibble, then bit 3 flipped: two's complement nibbles
+    *word_a = (wa - (0x4B400000u - 1u) * 0x11111111u) ^ 0x88888888u;
+    *word_b = (wb - (0x4B400000u - 1u) * 0x11111111u) ^ 0x88888888u;
 }
 
 // SiLU(gate) * up of 8 fp16 pairs -> 8 bf16 in one 16-byte register set.  fp32 throughout:
@@ -201,24 +227,20 @@ fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict
             mma_bf16_16816_first(acc[nt], xa.x, xb.x, xa.y, xb.y, bt[nt].x, bt[nt].y);
             mma_bf16_16816(acc[nt], xa.z, xb.z, xa.w, xb.w, bt[nt].z, bt[nt].w);
         }
-        float va[8], vb[8];
+        float2 va[4], vb[4];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
-            va[2 * nt] = acc[nt][0]; va[2 * nt + 1] = acc[nt][1];
-            vb[2 * nt] = acc[nt][2]; vb[2 * nt + 1] = acc[nt][3];
+            va[nt] = make_float2(acc[nt][0], acc[nt][1]);
+            vb[nt] = make_float2(acc[nt][2], acc[nt][3]);
         }
-        uint32_t wa, sa, wb, sb;
-        quantise_row_octet(va, &wa, &sa);                 // all lanes take part in the shuffles
-        quantise_row_octet(vb, &wb, &sb);
+        uint32_t wa, wb, sbits;
+        quantise_two_row_octets(va, vb, lane, &wa, &wb, &sbits);   // all lanes take part in the shuffles
         ra = r0 + gid; rb = ra + 8;
-        if (ra < r_end) {
-            q_out[((size_t)ra * C + g) * 4 + tig] = wa;
-            if (tig == 0) s_out[(size_t)ra * C + g] = __ushort_as_bfloat16((unsigned short)sa);
-        }
-        if (rb < r_end) {
-            q_out[((size_t)rb * C + g) * 4 + tig] = wb;
-            if (tig == 0) s_out[(size_t)rb * C + g] = __ushort_as_bfloat16((unsigned short)sb);
-        }
+        if (ra < r_end) q_out[((size_t)ra * C + g) * 4 + tig] = wa;
+        if (rb < r_end) q_out[((size_t)rb * C + g) * 4 + tig] = wb;
+        // lane 0 of the quad carries row a's scale, lane 1 row b's
+        const long long rs = tig == 0 ? ra : rb;
+        if (tig < 2 && rs < r_end) s_out[(size_t)rs * C + g] = __ushort_as_bfloat16((unsigned short)sbits);
         xa = nxa; xb = nxb;
     }
 }
