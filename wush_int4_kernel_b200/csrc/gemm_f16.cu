@@ -48,12 +48,12 @@ namespace {
 template <bool PERM>
 __global__ void __launch_bounds__(256)
 dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ s, __half* __restrict__ out,
-                   float* __restrict__ row_factor, long long rows, int K)
+                   float* __restrict__ row_factor, long long rows, int K, int wait_for_primary)
 {
     const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= rows) return;
     const int G = K >> 5;
+    const int warps = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * warps + (threadIdx.x >> 5); row < rows; row += (long long)gridDim.x * warps) {
     const unsigned short* sr = reinterpret_cast<const unsigned short*>(s) + row * G;
     // largest scale of the row (bf16 bit patterns of non-negative values order like integers)
     unsigned mx = 0;
@@ -87,6 +87,11 @@ dequant_f16_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* __restric
 #pragma unroll
         for (int i = 0; i < 4; ++i) orow[g * 4 + i] = o[i];
     }
+    }
+    // Launched as a programmatic dependent of a kernel it does not depend on (it widens the weights of
+    // later column tiles while that kernel multiplies the first ones): it must not COMPLETE before that
+    // kernel has, because whatever follows in the stream is ordered behind this grid only.
+    if (wait_for_primary) pdl_wait();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -604,7 +609,8 @@ constexpr int T_TOTAL = T_BARS + (2 * T_STAGES + 2 + 1) * 8 + 16 + 1024;
 template <bool I8>
 __global__ void __launch_bounds__(T_THREADS, 1)
 gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TileScale sc,
-                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err,
+                      int tile_n_first, int tile_n_count)                     // the column tiles this launch covers
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -616,9 +622,12 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
+    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), n_tiles = tiles_m * tile_n_count;
     const int k_steps = K / (I8 ? 128 : 64);                 // a stage row is 128 bytes either way
 
+    // A dependent launched behind this grid (the widening of the next column tiles) may start as soon as
+    // every CTA is resident: it runs in the threads and registers this kernel leaves free.
+    pdl_launch_dependents();
     if (tid == 0) {
         for (int i = 0; i < T_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
         tc::mbar_init(acc_full, 1);
@@ -642,7 +651,7 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int issued = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
+                const int m0 = (t % tiles_m) * 2 * FM, n0 = (tile_n_first + t / tiles_m) * FN;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
                     uint8_t* st = smem + slot * T_STAGE;
@@ -702,7 +711,7 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t aphase = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
+            const int m0 = (t % tiles_m) * 2 * FM, n0 = (tile_n_first + t / tiles_m) * FN;
             if (!tc::mbar_wait(acc_full, aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -877,7 +886,7 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
         cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
         if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
     }
-    dequant_f16_kernel<true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
+    dequant_f16_kernel<true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K, 0);
     row_shift_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)ws, fb, dn, (long long)N, (int)(K / 32));
     if (int s = check_launch("f16 pre-pass")) return s;
     CUtensorMap ma, mp;
@@ -934,19 +943,56 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
         cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
         if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
     }
-    dequant_f16_kernel<false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K);
-    dequant_f16_kernel<false><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, (const __nv_bfloat16*)ws, b16, fb, (long long)N, (int)K);
+    const __nv_bfloat16* ws16 = (const __nv_bfloat16*)ws;
+    dequant_f16_kernel<false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(xq, (const __nv_bfloat16*)xs, a16, fa, (long long)M, (int)K, 0);
+    if (use_pair_tiles(false)) {
+        dequant_f16_kernel<false><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(wq, ws16, b16, fb, (long long)N, (int)K, 0);
+        if (int s = check_launch("dequant_f16")) return s;
+        return pair_launch(false, a16, b16, fa, fb, 0.f, nullptr, y, M, N, K, err, st);
+    }
+    // The weight pre-pass is a tenth of the whole product at prefill sizes (N = 57344, K = 8192: 268 us of 2.87 ms,
+    // 1.2 GB moved) and bound by HBM, while the GEMM is bound by the tensor pipe and the power cap.  So only the
+    // first `head` column tiles are widened up front -- as many as make whole waves of tiles --; the rest is
+    // widened by a programmatic dependent of the GEMM over those tiles, in the threads and registers the
+    // persistent GEMM CTAs leave free, and a second GEMM launch takes the remaining column tiles.
+    const int tiles_m = (int)((M + 2 * FM - 1) / (2 * FM)), tiles_n = (int)((N + FN - 1) / FN);
+    int head = tiles_n;
+    {
+        int a = tiles_m, b = sm_count();
+        while (b) { const int t = a % b; a = b; b = t; }                 // a = gcd(tiles_m, multiprocessors)
+        const int wave_cols = sm_count() / a;                             // column tiles that make whole waves
+        const char* v = std::getenv("WUSH_PREPASS_OVERLAP");              // 0 switches the overlap off (measurements)
+        if (!(v && v[0] == '0') && tiles_n >= 3 * wave_cols) head = wave_cols;
+    }
+    const long long head_rows = std::min<long long>((long long)head * FN, N);
+    dequant_f16_kernel<false><<<(unsigned)((head_rows + 7) / 8), 256, 0, st>>>(wq, ws16, b16, fb, head_rows, (int)K, 0);
     if (int s = check_launch("dequant_f16")) return s;
-    if (use_pair_tiles(false)) return pair_launch(false, a16, b16, fa, fb, 0.f, nullptr, y, M, N, K, err, st);
     CUtensorMap ma, mb;
     int s;
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b16, K, N, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
-    const int64_t tiles = ((M + 2 * FM - 1) / (2 * FM)) * ((N + FN - 1) / FN);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const TileScale sc = {fa, fb, 0.f, nullptr};
-    gemm_tile2_kernel<false><<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
-    return check_launch("gemm_f16");
+    const int64_t tiles_head = (int64_t)tiles_m * head;
+    gemm_tile2_kernel<false><<<(int)std::min<int64_t>(tiles_head, sm_count()), T_THREADS, T_TOTAL, st>>>(
+        ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, 0, head);
+    if ((s = check_launch("gemm_f16"))) return s;
+    if (head < tiles_n) {
+        const long long rest = N - head_rows;
+        // One CTA of 8 warps per multiprocessor, all resident beside the GEMM (measured, whole product in us at
+        // M = 4096, N = 57344, K = 8192, no overlap 2854-2979: 8 warps 2763-2873, 16 warps 2798, 4 warps 2924,
+        // 2 warps 3390 -- too slow, the second GEMM waits --, two CTAs of 8 warps 3270: the GEMM's single
+        // issuing threads and its TMA loads suffer; streaming-store hints changed nothing).
+        const long long ctas = std::min<long long>((rest + 7) / 8, (long long)sm_count());
+        cudaError_t e = launch_dependent(dequant_f16_kernel<false>, dim3((unsigned)ctas), dim3(256), (size_t)0, st,
+                                         wq + (size_t)head_rows * (K / 2), ws16 + (size_t)head_rows * (K / 32),
+                                         b16 + (size_t)head_rows * K, fb + head_rows, rest, (int)K, 1);
+        if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "dequant_f16 (overlapped) launch: %s", cudaGetErrorString(e));
+        const int64_t tiles_rest = (int64_t)tiles_m * (tiles_n - head);
+        gemm_tile2_kernel<false><<<(int)std::min<int64_t>(tiles_rest, sm_count()), T_THREADS, T_TOTAL, st>>>(
+            ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, head, tiles_n - head);
+        if ((s = check_launch("gemm_f16"))) return s;
+    }
+    return WUSH_OK;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1014,7 +1060,8 @@ int i8_tile_dispatch(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N,
     const int64_t tiles = ((M + 2 * FM - 1) / (2 * FM)) * ((N + FN - 1) / FN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const TileScale sc = {nullptr, nullptr, alpha, alpha_dev};
-    gemm_tile2_kernel<true><<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err);
+    gemm_tile2_kernel<true><<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, 0,
+                                                              (int)((N + FN - 1) / FN));
     return check_launch("gemm_i8_tile");
 }
 
