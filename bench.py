@@ -222,7 +222,7 @@ def measure_ffn_block(world, rank, dev):
     from wush_int4_kernel_b200.peer_reduce import PeerAllReduce
 
     layers = bench_matrix.build_ffn_layers(world, rank, dev, copies=3)
-    peer = PeerAllReduce(max_elements=max(64 * 8192, 32 * 57344 // world))   # 64 rows of the block's output; a 32-row block of the gate+up shard
+    peer = PeerAllReduce(max_elements=2048 * 8192)   # the block's output at every M measured (two-phase sum beyond a megabyte); 32-row blocks of the gate+up shard
     out = {}
     for m in (1, 32, 2048):
         with_peer = bench_matrix.measure_ffn(m, world, rank, dev, True, peer, layers=layers)

@@ -223,6 +223,12 @@ int wush_w4a4_gemm_tensor_scale_ws(const uint8_t* xq, const uint8_t* wq, int64_t
  *                      2n <= slot_bytes; every rank must call it the same number of times with the
  *                      same n.  One kernel launch, no host synchronisation, capturable; a rank waits for
  *                      its peers inside the kernel for about a second at most, then records an error;
+ *   wush_comm_allreduce_two_phase_f16   the same sum, same result bit for bit, as a reduce-scatter and an
+ *                      all-gather inside one kernel (it takes TWO steps of the communicator): rank r sums
+ *                      its 1/world share of all ranks' partials and stores the result into every rank's
+ *                      buffer.  (world-1)/world of the data crosses NVLink per direction instead of
+ *                      (world-1) times the data being read: the form for results of a megabyte and more
+ *                      (prefill), where the library all-reduce of an fp32 copy is the alternative;
  *   wush_comm_gemv_allreduce   decode product (the operands of wush_w4a4_gemm; M <= 2 by the CUDA-core
  *                      GEMV, M <= 32 with K % 256 == 0 by the streaming kernel) AND the sum over ranks: the product kernel's epilogue stores its fp16 result into every rank's
  *                      buffer over NVLink and its last CTA publishes the step; the reduction then reads
@@ -252,6 +258,7 @@ int wush_comm_connect_pointer(void* comm, int peer_rank, void* peer_base);
 int wush_comm_base(void* comm, void** base);
 int wush_comm_set_poll_limit(void* comm, unsigned int polls);
 int wush_comm_allreduce_f16(void* comm, const void* partial, void* out, int64_t n, void* stream);
+int wush_comm_allreduce_two_phase_f16(void* comm, const void* partial, void* out, int64_t n, void* stream);
 int wush_comm_gemv_allreduce(void* comm, const uint8_t* xq, const void* xs, const uint8_t* wq,
                              const void* ws, int64_t M, int64_t N, int64_t K, void* out, void* stream);
 int wush_comm_allgather_f16(void* comm, const void* local, void* out, int64_t rows, const int64_t* widths,

@@ -107,3 +107,17 @@ def tile_selftest(a, b, layout_mode: int = 0):
     capi.check(lib.wush_i8_tile_selftest(a.data_ptr(), b.data_ptr(), d.data_ptr(), n, layout_mode, status.data_ptr(),
                                          _stream()), "tile_selftest")
     return d, int(status.item())
+
+
+class _RawDeviceMemory:
+    """Wraps a raw device pointer so that torch can view it (CUDA array interface, version 2)."""
+
+    def __init__(self, ptr: int, count: int, typestr: str):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def device_view(ptr: int, count: int, dtype: torch.dtype) -> torch.Tensor:
+    """A tensor over `count` elements of device memory at `ptr` (no copy): for tests that look into the
+    exchange buffers of a communicator."""
+    typestr = {torch.float16: "<f2", torch.float32: "<f4", torch.uint8: "|u1", torch.int32: "<i4"}[dtype]
+    return torch.as_tensor(_RawDeviceMemory(ptr, count, typestr), device="cuda")

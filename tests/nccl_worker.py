@@ -42,6 +42,18 @@ def main():
             acc = acc + g.float()
         got = peer(part)
         assert torch.equal(got, acc.to(torch.float16)), f"peer all-reduce differs at step {step}"
+    # results of megabytes take the two-phase kernel (reduce-scatter + all-gather): same bits, mixed with small steps
+    big = PeerAllReduce(max_elements=1024 * 768)
+    for step, rows in enumerate([1024, 6, 1000, 1024]):
+        part = torch.randn(rows, 768, generator=gen_r, device="cuda").to(torch.float16)
+        gathered = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(gathered, part)
+        acc = torch.zeros(rows, 768, device="cuda")
+        for g in gathered:
+            acc = acc + g.float()
+        assert torch.equal(big(part), acc.to(torch.float16)), f"two-phase all-reduce differs at step {step}"
+    assert big.error() == 0
+    big.close()
     part = torch.randn(8, 768, generator=gen_r, device="cuda").to(torch.float16)
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()

@@ -306,3 +306,66 @@ def test_peer_allgather_two_ranks_one_after_the_other(setup, M):
         finally:
             for c in comms:
                 capi.check(lib.wush_comm_destroy(c), "comm_destroy")
+
+
+def test_peer_allreduce_two_phase_single_rank_and_sequential_ranks():
+    """The two-phase sum (reduce-scatter + all-gather in one kernel).  World of one: the result is the
+    input.  World of two in one process, the ranks' kernels run one after the other: rank 1 first, whose
+    waits (~2 ms) run out with its partial and its flag in place; rank 0 then finds rank 1's partial,
+    reduces its own half exactly -- the half rank 1 would have delivered stays untouched -- and gives up
+    at the second wait (nobody publishes the second step for rank 1).  Checks addressing and bounded waits."""
+    import ctypes
+    from wush_int4_kernel_b200 import capi
+    lib = capi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    comm = ctypes.c_void_p()
+    capi.check(lib.wush_comm_create(0, 1, 4 << 20, ctypes.byref(comm)), "comm_create")
+    try:
+        for n in (8, 1 << 20, 8192, 2 << 20):
+            part = torch.randn(n, generator=gen, device="cuda").to(torch.float16)
+            out = torch.zeros_like(part)
+            capi.check(lib.wush_comm_allreduce_two_phase_f16(comm, part.data_ptr(), out.data_ptr(), n, stream), "two_phase")
+            assert torch.equal(out, part)
+            plain = torch.zeros_like(part)
+            capi.check(lib.wush_comm_allreduce_f16(comm, part.data_ptr(), plain.data_ptr(), n, stream), "allreduce")
+            assert torch.equal(plain, part)
+        err = ctypes.c_int(-1)
+        capi.check(lib.wush_comm_error(comm, ctypes.byref(err)), "comm_error")
+        assert err.value == 0
+    finally:
+        capi.check(lib.wush_comm_destroy(comm), "comm_destroy")
+
+    comms = [ctypes.c_void_p(), ctypes.c_void_p()]
+    for r in range(2):
+        capi.check(lib.wush_comm_create(r, 2, 1 << 20, ctypes.byref(comms[r])), "comm_create")
+    try:
+        for r in range(2):
+            base = ctypes.c_void_p()
+            capi.check(lib.wush_comm_base(comms[1 - r], ctypes.byref(base)), "comm_base")
+            capi.check(lib.wush_comm_connect_pointer(comms[r], 1 - r, base), "comm_connect_pointer")
+            capi.check(lib.wush_comm_set_poll_limit(comms[r], 4096), "comm_set_poll_limit")
+        n = 1 << 18
+        parts = [torch.randn(n, generator=gen, device="cuda").to(torch.float16) for _ in range(2)]
+        outs = [torch.full((n,), 7.0, dtype=torch.float16, device="cuda") for _ in range(2)]
+        for r in (1, 0):
+            capi.check(lib.wush_comm_allreduce_two_phase_f16(comms[r], parts[r].data_ptr(), outs[r].data_ptr(), n, stream), "two_phase")
+            torch.cuda.synchronize()
+        errs = []
+        for r in range(2):
+            e = ctypes.c_int(-1)
+            capi.check(lib.wush_comm_error(comms[r], ctypes.byref(e)), "comm_error")
+            errs.append(e.value)
+        assert errs == [1, 1]
+        assert bool((outs[0] == 7.0).all())                          # a sum that was not completed is not delivered
+        # rank 0's half of the sum reached rank 1's buffer: slot (1, 1) of rank 1, vectors [0, n/2)
+        base1 = ctypes.c_void_p()
+        capi.check(lib.wush_comm_base(comms[1], ctypes.byref(base1)), "comm_base")
+        expect = (parts[0].float() + parts[1].float()).to(torch.float16)[: n // 2]
+        from tests import cabi
+        got = cabi.device_view(base1.value + (1 * 2 + 1) * (1 << 20), n // 2, torch.float16)
+        assert torch.equal(got, expect)
+        assert torch.isfinite((parts[0] * 2).sum()).item()            # the device still computes
+    finally:
+        for c in comms:
+            capi.check(lib.wush_comm_destroy(c), "comm_destroy")

@@ -159,7 +159,9 @@ def measure_ffn(M: int, tp: int, rank: int, dev, distributed: bool, peer=None, l
         reduce_kind = "nccl fp32"
     else:
         pushed = M <= 2 or (M <= 32 and (il) % 256 == 0)
-        reduce_kind = "peer memory, pushed from the product kernel" if pushed else "peer memory, one kernel"
+        reduce_kind = ("peer memory, pushed from the product kernel" if pushed else
+                       "peer memory, reduce-scatter + all-gather in one kernel" if M * hidden * 2 >= peer.TWO_PHASE_BYTES else
+                       "peer memory, one kernel")
     return {"block": "ffn 8192 -> 2 x 28672 -> 8192", "M": M, "tp": tp, "all_reduce": reduce_kind, "graph": captured,
             "us_per_block": round(t, 2), "eff_tops_whole_block": round(ops_total / t / 1e6, 2),
             "weight_bytes_per_rank": wbytes, "weight_stream_gbs_per_rank": round(wbytes / t / 1e3, 1)}

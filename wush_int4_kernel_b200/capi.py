@@ -46,6 +46,7 @@ SIGNATURES = {
     "wush_comm_set_poll_limit": (_int, [_vp, ctypes.c_uint]),
     "wush_comm_allreduce_f16": (_int, [_vp, _vp, _vp, _i64, _vp]),
     "wush_comm_gemv_allreduce": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "wush_comm_allreduce_two_phase_f16": (_int, [_vp, _vp, _vp, _i64, _vp]),
     "wush_comm_allgather_f16": (_int, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "wush_comm_gemv_allgather": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "wush_comm_error": (_int, [_vp, ctypes.POINTER(_int)]),

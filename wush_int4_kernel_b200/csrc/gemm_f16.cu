@@ -827,7 +827,8 @@ bool f16_supported(int64_t M, int64_t N, int64_t K) { return M >= 1 && K % 64 ==
 
 // Rows up to which the weights are widened inside the GEMM (no fp16 copy of W in the scratch).  Measured at
 // K = 8192, N = 57344 (us, in-kernel widening vs weight pre-pass): M = 128: 209 vs 464, 256: 277 vs 529,
-// 512: 517 vs 664, 1024: 872 vs 983, 2048: 1714 vs 1789, 4096: 3516 vs 3267.
+// 512: 517 vs 664, 1024: 872 vs 983, 2048: 1714 vs 1789, 4096: 3516 vs 3267; with the weight pre-pass overlapped
+// with the GEMM (f16_dispatch): 512: 523 vs 766, 1024: 888 vs 1065, 1536: 1259 vs 1297, 2048: 1636 vs 1632.
 constexpr int64_t FUSED_MAX_ROWS = 2048;
 static bool use_fused(int64_t M, int64_t N, int64_t K) { return M <= FUSED_MAX_ROWS && K % 256 == 0; }   // whole 16-byte scale vectors
 

@@ -21,6 +21,7 @@ struct CommState {                                   // device resident
     unsigned int done;                               // CTAs that finished the reduction of the current step
     int error;                                       // 1 = a wait ran out
     unsigned int poll_limit;                         // polls after which a wait gives up
+    unsigned int copied2;                            // CTAs that finished the second phase of a two-phase step
 };
 
 struct PeerTable {                                   // kernel argument: the buffers of all ranks
@@ -54,9 +55,10 @@ __device__ __forceinline__ uint4 ld_sys_v4(const void* p) {            // system
 // Called by one full warp of every CTA once the CTA's share of the contribution is written and
 // fenced to system scope: counts the CTA, and the last one publishes step + 1 to all ranks
 // (lane r stores into rank r's flag array, so the remote stores overlap).
-__device__ __forceinline__ void comm_count_and_publish(const PeerTable& t, unsigned int step, int lane) {
+__device__ __forceinline__ void comm_count_and_publish(const PeerTable& t, unsigned int step, int lane,
+                                                       unsigned int* counter = nullptr) {
     unsigned int arrived = 0;
-    if (lane == 0) arrived = atomicAdd(&t.state->copied, 1u);
+    if (lane == 0) arrived = atomicAdd(counter ? counter : &t.state->copied, 1u);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
     if (arrived == gridDim.x - 1) {
         __threadfence_system();

@@ -101,11 +101,101 @@ __device__ __forceinline__ void exchange_end(const PeerTable& peers, unsigned in
         const unsigned int finished = atomicAdd(&state->done, 1u);
         if (finished == gridDim.x - 1) {
             state->copied = 0;
+            state->copied2 = 0;
             state->done = 0;
             __threadfence();
             state->step = step + 1u;
         }
     }
+}
+
+// Bounded wait of warp 0 until every rank has published `target` steps; all threads get the verdict.
+__device__ __forceinline__ bool wait_all_published(const PeerTable& peers, unsigned int target)
+{
+    __shared__ unsigned int s_ok2;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const unsigned int poll_limit = *reinterpret_cast<volatile unsigned int*>(&peers.state->poll_limit);
+        bool ok = true;
+        if (lane < peers.world) {
+            uint32_t polls = 0;
+            while ((int)(ld_acquire_sys(peers.flags[peers.rank] + lane) - target) < 0) {
+                if (++polls > poll_limit) { ok = false; break; }
+                __nanosleep(polls < 64 ? 20 : 500);
+            }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) {
+            if (!ok) atomicExch(&peers.state->error, 1);
+            s_ok2 = ok ? 1u : 0u;
+        }
+    }
+    __syncthreads();
+    return s_ok2 != 0;
+}
+
+// Two-phase sum for results of megabytes (prefill): a reduce-scatter and an all-gather over peer memory in ONE
+// kernel, two steps of the communicator.  Step s: every rank puts its partial into its own slot (s & 1, rank)
+// and publishes; rank r then sums vectors [r n/world, (r+1) n/world) of all ranks' slots in rank order (peer
+// loads, fp32) and stores the fp16 result into slot ((s+1) & 1, p) of EVERY rank p (remote stores).  Step
+// s + 1: publish, wait, copy the own slot ((s+1) & 1, rank) to the output.  Per rank (world-1)/world of the
+// data crosses NVLink in each direction, against (world-1) times the data read by the one-phase kernel; the
+// result is the same bit for bit (same summation order).
+__global__ void __launch_bounds__(PR_THREADS)
+peer_allreduce_two_phase_f16_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, long long n_vec, const PeerTable peers)
+{
+    const int rank = peers.rank, world = peers.world;
+    const long long stride = (long long)gridDim.x * PR_THREADS;
+    const long long first = (long long)blockIdx.x * PR_THREADS + threadIdx.x;
+    unsigned int step;
+    bool ok = exchange_begin(local, n_vec, peers, 0, &step);
+
+    if (ok) {                                                          // reduce-scatter: this rank's share
+        const long long c0 = n_vec * rank / world, c1 = n_vec * (rank + 1) / world;
+        for (long long i = c0 + first; i < c1; i += stride) {
+            uint4 v[PR_MAX_WORLD];
+#pragma unroll
+            for (int r = 0; r < PR_MAX_WORLD; ++r) {
+                const int src = r < world ? r : rank;
+                v[r] = ld_sys_v4(reinterpret_cast<const uint4*>(peers.base[src] + slot_offset(peers, step, src)) + i);
+            }
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+            for (int r = 0; r < PR_MAX_WORLD; ++r) {
+                if (r < world) {
+                    const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[p]));
+                        acc[2 * p] += f.x;
+                        acc[2 * p + 1] += f.y;
+                    }
+                }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                __half2 h = __floats2half2_rn(acc[2 * p], acc[2 * p + 1]);
+                o[p] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            const uint4 res = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+            for (int p = 0; p < PR_MAX_WORLD; ++p)
+                if (p < world) reinterpret_cast<uint4*>(peers.base[p] + slot_offset(peers, step + 1u, p))[i] = res;
+        }
+    }
+    // second step: this rank's share is in every rank's buffer -> publish, wait for everybody's
+    __threadfence_system();
+    __syncthreads();
+    if (ok && threadIdx.x < 32) comm_count_and_publish(peers, step + 1u, threadIdx.x, &peers.state->copied2);   // a rank that did not see every partial delivers nothing
+    ok = wait_all_published(peers, step + 2u) && ok;
+    if (ok) {
+        const uint4* mine = reinterpret_cast<const uint4*>(peers.base[rank] + slot_offset(peers, step + 1u, rank));
+        for (long long i = first; i < n_vec; i += stride) out[i] = ld_sys_v4(mine + i);
+    }
+    exchange_end(peers, step + 1u);
 }
 
 __global__ void __launch_bounds__(PR_THREADS)
@@ -228,6 +318,17 @@ int launch_reduce(const Comm* c, const PeerTable& t, const void* partial, void* 
     return WUSH_OK;
 }
 
+int launch_reduce_two_phase(const Comm* c, const PeerTable& t, const void* partial, void* out, int64_t n, cudaStream_t st)
+{
+    const long long n_vec = n / 8;
+    long long blocks = (n_vec + PR_THREADS - 1) / PR_THREADS;
+    if (blocks > sm_count()) blocks = sm_count();                       // every CTA resident while it waits
+    cudaError_t e = launch_dependent(peer_allreduce_two_phase_f16_kernel, dim3((unsigned)blocks), dim3(PR_THREADS), (size_t)0, st,
+                                     (const uint4*)partial, (uint4*)out, n_vec, t);
+    if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "comm_allreduce (two-phase) launch: %s", cudaGetErrorString(e));
+    return WUSH_OK;
+}
+
 int gather_shape(const Comm* c, const int64_t* widths, int64_t rows, GatherShape* g, const char* what)
 {
     if (!widths) return fail(WUSH_ERR_INVALID_ARGUMENT, "%s: null widths", what);
@@ -277,7 +378,7 @@ WUSH_API int wush_comm_create(int rank, int world, size_t slot_bytes, void** com
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), comm_bytes(c));
     if (e == cudaSuccess) e = cudaMemset(c->base, 0, comm_bytes(c));
     if (e == cudaSuccess) {
-        CommState init = {0, 0, 0, 0, PR_POLL_LIMIT};
+        CommState init = {0, 0, 0, 0, PR_POLL_LIMIT, 0};
         e = cudaMemcpy(c->base + slots_bytes(c) + PR_FLAG_BYTES, &init, sizeof(init), cudaMemcpyHostToDevice);
     }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -366,6 +467,23 @@ WUSH_API int wush_comm_allreduce_f16(void* comm, const void* partial, void* out,
     PeerTable t;
     if (int s = fill_table(c, &t, "comm_allreduce")) return s;
     return launch_reduce(c, t, partial, out, n, 0, (cudaStream_t)stream);
+}
+
+// The same sum as reduce-scatter + all-gather in one kernel (two steps of the communicator): for results of a
+// megabyte and more, where the one-phase kernel's (world - 1) reads of everything cost more than a second wait.
+WUSH_API int wush_comm_allreduce_two_phase_f16(void* comm, const void* partial, void* out, int64_t n, void* stream)
+{
+    using namespace wush;
+    WUSH_REQUIRE(comm, "comm_allreduce_two_phase: null communicator");
+    Comm* c = static_cast<Comm*>(comm);
+    WUSH_REQUIRE(n >= 0 && n % 8 == 0, "comm_allreduce_two_phase: element count must be a multiple of 8");
+    if (n == 0) return WUSH_OK;
+    WUSH_REQUIRE(partial && out && aligned16(partial) && aligned16(out), "comm_allreduce_two_phase: pointers must be 16-byte aligned");
+    WUSH_REQUIRE((size_t)n * 2 <= c->slot_bytes, "comm_allreduce_two_phase: %lld halves do not fit the slot of %zu bytes", (long long)n,
+                 c->slot_bytes);
+    PeerTable t;
+    if (int s = fill_table(c, &t, "comm_allreduce_two_phase")) return s;
+    return launch_reduce_two_phase(c, t, partial, out, n, (cudaStream_t)stream);
 }
 
 // Decode product and the sum over ranks as one chain of two kernels that share the exchange: the

@@ -18,6 +18,8 @@ from . import capi
 
 
 class PeerAllReduce:
+    TWO_PHASE_BYTES = 1 << 20
+
     def __init__(self, max_elements: int, group=None):
         import torch.distributed as dist
 
@@ -47,8 +49,11 @@ class PeerAllReduce:
         if not self.fits(partial):
             raise ValueError("PeerAllReduce: needs a contiguous CUDA fp16 tensor of a multiple of 8 elements that fits the slot")
         out = torch.empty_like(partial)
-        capi.check(self.lib.wush_comm_allreduce_f16(self.comm, partial.data_ptr(), out.data_ptr(), partial.numel(),
-                                                    torch.cuda.current_stream().cuda_stream), "comm_allreduce_f16")
+        # a megabyte and more: reduce-scatter + all-gather in one kernel instead of every rank reading everything
+        two_phase = self.world > 1 and partial.numel() * 2 >= self.TWO_PHASE_BYTES
+        fn = self.lib.wush_comm_allreduce_two_phase_f16 if two_phase else self.lib.wush_comm_allreduce_f16
+        capi.check(fn(self.comm, partial.data_ptr(), out.data_ptr(), partial.numel(), torch.cuda.current_stream().cuda_stream),
+                   "comm_allreduce_f16")
         return out
 
     def product_allreduce(self, xq, xs, wq, ws):
