@@ -166,7 +166,7 @@ def run_reference_arm(args):
 def measure_prefill(weights, t_bf16, outliers, gen, dev, world, n_local, barrier):
     """M = PREFILL_ROWS rows through the same layer (this rank's column shard): transform+quantise, then
     the product through the public op (my_int4._C.w4a4_gemm_s4).  Median of 5 batches of 4 graph replays
-    over the rotating weight copies, max over ranks."""
+    over the rotating weight copies (layer and product batches alternating), max over ranks."""
     import torch
     import torch.distributed as dist
 
@@ -178,29 +178,34 @@ def measure_prefill(weights, t_bf16, outliers, gen, dev, world, n_local, barrier
     xq, xs = quantise_activations(x, t_bf16)
     use = weights[:2]
 
-    def median_ms(graphs):
-        for i in range(3):
+    def batch_ms(graphs):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(4):
             graphs[i % len(graphs)].replay()
-        out = []
-        for _ in range(5):
-            barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(4):
-                graphs[i % len(graphs)].replay()
-            e1.record()
-            torch.cuda.synchronize()
-            out.append(e0.elapsed_time(e1) / 4)
-        ms = statistics.median(out)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 4
+
+    def across_ranks(ms):
         if world > 1:
             tmax = torch.tensor([ms], device=dev)
             dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
             ms = float(tmax.item())
         return ms
 
-    layer_ms = median_ms([timing.capture(lambda wq=wq, ws=ws: w4a4_product(*quantise_activations(x, t_bf16), wq, ws))[0]
-                          for (wq, ws) in use])
-    prod_ms = median_ms([timing.capture(lambda wq=wq, ws=ws: w4a4_product(xq, xs, wq, ws))[0] for (wq, ws) in use])
+    layer_graphs = [timing.capture(lambda wq=wq, ws=ws: w4a4_product(*quantise_activations(x, t_bf16), wq, ws))[0]
+                    for (wq, ws) in use]
+    prod_graphs = [timing.capture(lambda wq=wq, ws=ws: w4a4_product(xq, xs, wq, ws))[0] for (wq, ws) in use]
+    for i in range(3):
+        layer_graphs[i % len(layer_graphs)].replay()
+    # batches of the two graphs alternate, so both medians see the same power / clock state of the part
+    layer_t, prod_t = [], []
+    for _ in range(5):
+        layer_t.append(batch_ms(layer_graphs))
+        prod_t.append(batch_ms(prod_graphs))
+    layer_ms, prod_ms = across_ranks(statistics.median(layer_t)), across_ranks(statistics.median(prod_t))
     torch.cuda.empty_cache()
     tpeak, tkind = measured_peak("bf16_tflops", 1590.0)
     per_gpu = 2.0 * M * n_local * K_DIM / (prod_ms * 1e-3) / 1e12
