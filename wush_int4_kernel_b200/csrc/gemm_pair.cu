@@ -201,6 +201,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const int n = n0 + c * 32;
                 if (m < M && n < N) {
                     __half* yr = y + (size_t)m * N + n;
+                    const bool wide = ((reinterpret_cast<uintptr_t>(y) & 31) == 0) && (N & 15) == 0;   // 32-byte stores possible
+                    uint4 prev = make_uint4(0, 0, 0, 0);
 #pragma unroll
                     for (int v8 = 0; v8 < 4; ++v8) {
                         if (n + v8 * 8 + 8 <= N) {
@@ -223,7 +225,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                     o[p] = *reinterpret_cast<uint32_t*>(&h);
                                 }
                             }
-                            *reinterpret_cast<uint4*>(yr + v8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                            const uint4 cur = make_uint4(o[0], o[1], o[2], o[3]);
+                            if (!wide) *reinterpret_cast<uint4*>(yr + v8 * 8) = cur;
+                            else if (v8 & 1) st_global_v8(yr + (v8 - 1) * 8, prev, cur);
+                            else prev = cur;
                         }
                     }
                 }
