@@ -26,6 +26,8 @@
 //
 // Algorithmic HBM bytes: 2*M*K (x) + 64*K (T, read once, L2 resident after) + M*K/2 (codes)
 // + M*K/16 (scales).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace wush {
@@ -168,12 +170,15 @@ __device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g2, uint32_t u2) {
 
 // 8 consecutive inputs of row r for this lane.  SILU: `x` is the fp16 output of a fused gate+up
 // projection, (rows, 2K) with the gate half first; the activation is computed on the fly.
+// 8 consecutive inputs of one row for this lane, `p` pointing at them.  SILU: `p` points into the gate half of
+// the fp16 output of a fused gate+up projection, (rows, 2K) with the gate half first and the up half K elements
+// (C * 32) further; the activation is computed on the fly.
 template <bool SILU>
-__device__ __forceinline__ uint4 load_octet(const void* x, long long r, int C, int g, int tig) {
+__device__ __forceinline__ uint4 load_octet(const void* p, int C) {
     if constexpr (!SILU) {
-        return ldg_nc_v4(reinterpret_cast<const __nv_bfloat16*>(x) + ((size_t)r * C + g) * 32 + tig * 8);
+        return ldg_nc_v4(p);
     } else {
-        const __half* gate = reinterpret_cast<const __half*>(x) + ((size_t)r * 2 * C + g) * 32 + tig * 8;
+        const __half* gate = reinterpret_cast<const __half*>(p);
         const uint4 gv = ldg_nc_v4(gate), uv = ldg_nc_v4(gate + (size_t)C * 32);
         return make_uint4(silu_mul_pair(gv.x, uv.x), silu_mul_pair(gv.y, uv.y), silu_mul_pair(gv.z, uv.z),
                           silu_mul_pair(gv.w, uv.w));
@@ -199,7 +204,7 @@ fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict
     pdl_wait();
     if (g >= C) return;                                   // whole warp leaves together
     const long long r_begin = (long long)blockIdx.y * rows_per_cta;
-    const long long r_end = min(rows, r_begin + rows_per_cta);
+    int left = (int)(min(rows, r_begin + rows_per_cta) - r_begin);      // rows of this CTA not yet done
 
     // B operand: T[g] rows in the permuted order j(nt, n) = 8*(n>>1) + 2*nt + (n&1), n = gid.
     uint4 bt[4];
@@ -209,17 +214,35 @@ fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict
         bt[nt] = *reinterpret_cast<const uint4*>(t + (size_t)g * 1024 + j * 32 + tig * 8);
     }
 
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    // Running pointers of this lane (row gid of the slab; row gid + 8 sits a fixed distance further): 64-bit index
+    // arithmetic per access was a fifth of the loop's instructions.
+    constexpr int XE = SILU ? 2 : 1;                      // input elements per output element and row (gate | up)
+    const size_t x_row = (size_t)C * 32 * XE * 2;         // bytes per input row (2-byte elements)
+    const uint8_t* xp = reinterpret_cast<const uint8_t*>(x) + (size_t)(r_begin + gid) * x_row + ((size_t)g * 32 + tig * 8) * 2;
+    uint32_t* qp = q_out + ((size_t)(r_begin + gid) * C + g) * 4 + tig;
+    // lane 0 of a quad stores row a's scale, lane 1 row b's
+    __nv_bfloat16* sp = s_out + (size_t)(r_begin + gid + (tig == 1 ? 8 : 0)) * C + g;
+    const size_t x_half = 8 * x_row, x_slab = 16 * x_row;
+    const size_t q_half = (size_t)8 * C * 4, q_slab = (size_t)16 * C * 4, s_slab = (size_t)16 * C;
+    const int s_row = gid + (tig == 1 ? 8 : 0);
 
-    long long r0 = r_begin;
-    long long ra = r0 + gid, rb = ra + 8;
-    uint4 xa = ra < r_end ? load_octet<SILU>(x, ra, C, g, tig) : zero4;
-    uint4 xb = rb < r_end ? load_octet<SILU>(x, rb, C, g, tig) : zero4;
-    for (; r0 < r_end; r0 += 16) {
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    uint4 xa = gid < left ? load_octet<SILU>(xp, C) : zero4;
+    uint4 xb = gid + 8 < left ? load_octet<SILU>(xp + x_half, C) : zero4;
+    for (; left > 0; left -= 16) {
         // prefetch the next slab while this one is in the tensor core
-        const long long na = r0 + 16 + gid, nb = na + 8;
-        uint4 nxa = na < r_end ? load_octet<SILU>(x, na, C, g, tig) : zero4;
-        uint4 nxb = nb < r_end ? load_octet<SILU>(x, nb, C, g, tig) : zero4;
+        xp += x_slab;
+        // (pulling further slabs towards L2 with prefetch instructions changed nothing: 28.5 us at M = 4096, K = 8192
+        // with or without; nor did cutting the instruction count from 19.4 M to 11.5 M, nor CTAs of 16 or 32 warps that read 1 or
+        // 2 KB of a row at a time -- a warp needs about 1.7 us per slab whatever is done around it)
+        uint4 nxa, nxb;
+        if (left >= 32) {                                 // the common case: a whole next slab
+            nxa = load_octet<SILU>(xp, C);
+            nxb = load_octet<SILU>(xp + x_half, C);
+        } else {
+            nxa = gid + 16 < left ? load_octet<SILU>(xp, C) : zero4;
+            nxb = gid + 24 < left ? load_octet<SILU>(xp + x_half, C) : zero4;
+        }
 
         float acc[4][4];
 #pragma unroll
@@ -235,12 +258,17 @@ fused_tq_fast_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict
         }
         uint32_t wa, wb, sbits;
         quantise_two_row_octets(va, vb, lane, &wa, &wb, &sbits);   // all lanes take part in the shuffles
-        ra = r0 + gid; rb = ra + 8;
-        if (ra < r_end) q_out[((size_t)ra * C + g) * 4 + tig] = wa;
-        if (rb < r_end) q_out[((size_t)rb * C + g) * 4 + tig] = wb;
-        // lane 0 of the quad carries row a's scale, lane 1 row b's
-        const long long rs = tig == 0 ? ra : rb;
-        if (tig < 2 && rs < r_end) s_out[(size_t)rs * C + g] = __ushort_as_bfloat16((unsigned short)sbits);
+        if (left >= 16) {
+            qp[0] = wa;
+            qp[q_half] = wb;
+            if (tig < 2) *sp = __ushort_as_bfloat16((unsigned short)sbits);
+        } else {
+            if (gid < left) qp[0] = wa;
+            if (gid + 8 < left) qp[q_half] = wb;
+            if (tig < 2 && s_row < left) *sp = __ushort_as_bfloat16((unsigned short)sbits);
+        }
+        qp += q_slab;
+        sp += s_slab;
         xa = nxa; xb = nxb;
     }
 }
@@ -252,7 +280,14 @@ static int launch_fast(const void* x, const void* t, int64_t rows, int64_t C, ui
     int warps, rows_per_cta;
     if (rows <= 32) { warps = 2; rows_per_cta = 32; }
     else if (rows <= 512) { warps = 4; rows_per_cta = 64; }
-    else { warps = 8; rows_per_cta = 128; }
+    else {
+        // one balanced wave: four CTAs of 8 warps (64 registers per thread) are resident per multiprocessor; with
+        // 128 rows per CTA, M = 4096 and K = 8192 made 1024 CTAs for 592 places (two rounds, the second 73 % full)
+        warps = 8;
+        const int64_t gx = (C + warps - 1) / warps, places = 4LL * sm_count();
+        const int64_t gy_wave = std::max<int64_t>(1, places / gx);
+        rows_per_cta = (int)std::max<int64_t>(128, ((rows + gy_wave - 1) / gy_wave + 15) / 16 * 16);
+    }
     const int64_t gy = (rows + rows_per_cta - 1) / rows_per_cta;
     WUSH_REQUIRE(gy <= 65535, "fused_tq: too many rows");
     dim3 grid((unsigned)((C + warps - 1) / warps), (unsigned)gy);
