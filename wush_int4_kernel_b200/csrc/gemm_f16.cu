@@ -830,7 +830,8 @@ splitk_reduce_kernel(const float4* __restrict__ part, uint4* __restrict__ y, lon
 
 int pair_set_attributes();
 int pair_launch(bool i8, const void* a, const void* b, const float* fa, const float* fb, float alpha, const float* alpha_dev,
-                void* y, int64_t M, int64_t N, int64_t K, int* err, cudaStream_t st);
+                void* y, int64_t M, int64_t N, int64_t K, int* err, cudaStream_t st, int tile_n_first = 0, int tile_n_count = -1);
+int pairs_resident();
 
 // Which tile kernel the pre-widened routes run on.  Measured A/B on one B200, M = 4096, N = 57344, K = 8192, whole op
 // (us, burst of 3 calls / mean of 100 back-to-back calls under the 1 kW power cap):
@@ -1042,7 +1043,8 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
 // scales once in the epilogue -- the shape in which the int8 tensor path runs near its peak.
 namespace {
 __global__ void __launch_bounds__(256)
-widen_s8_kernel(const uint4* __restrict__ q, uint4* __restrict__ out, long long n_vec)     // 32 codes per step
+widen_s8_kernel(const uint4* __restrict__ q, uint4* __restrict__ out, long long n_vec,     // 32 codes per step
+                int wait_for_primary)       // launched beside a GEMM it does not depend on: do not complete before it has
 {
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
@@ -1065,6 +1067,7 @@ widen_s8_kernel(const uint4* __restrict__ q, uint4* __restrict__ out, long long 
             out[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
     }
+    if (wait_for_primary) pdl_wait();
 }
 }  // namespace
 
@@ -1092,10 +1095,37 @@ int i8_tile_dispatch(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N,
     if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
     const long long cap = (long long)sm_count() * 16;
     const long long va = M * K / 32, vb = N * K / 32;
-    widen_s8_kernel<<<(unsigned)std::min<long long>((va + 255) / 256, cap), 256, 0, st>>>((const uint4*)xq, (uint4*)a8, va);
-    widen_s8_kernel<<<(unsigned)std::min<long long>((vb + 255) / 256, cap), 256, 0, st>>>((const uint4*)wq, (uint4*)b8, vb);
+    widen_s8_kernel<<<(unsigned)std::min<long long>((va + 255) / 256, cap), 256, 0, st>>>((const uint4*)xq, (uint4*)a8, va, 0);
+    if (use_pair_tiles(true)) {
+        // As in the fp16-folded product: widen the weights of the first whole waves of column tiles, multiply
+        // them, and widen the rest beside that GEMM (a programmatic dependent with one CTA per multiprocessor).
+        const int tiles_m = (int)((M + 2 * FM - 1) / (2 * FM)), tiles_n = (int)((N + FN - 1) / FN);
+        int head = tiles_n;
+        {
+            const int wave = std::max(1, pairs_resident());
+            int a = tiles_m, b = wave;
+            while (b) { const int t = a % b; a = b; b = t; }
+            const int wave_cols = wave / a;                                  // column tiles that make whole waves
+            const char* v = std::getenv("WUSH_PREPASS_OVERLAP");
+            if (!(v && v[0] == '0') && tiles_n >= 3 * wave_cols) head = wave_cols;
+        }
+        const long long head_rows = std::min<long long>((long long)head * FN, N), vh = head_rows * K / 32;
+        widen_s8_kernel<<<(unsigned)std::min<long long>((vh + 255) / 256, cap), 256, 0, st>>>((const uint4*)wq, (uint4*)b8, vh, 0);
+        if (int s = check_launch("widen_s8")) return s;
+        if (int s = pair_launch(true, a8, b8, nullptr, nullptr, alpha, alpha_dev, y, M, N, K, err, st, 0, head)) return s;
+        if (head < tiles_n) {
+            const long long vr = vb - vh;
+            // (whole product at M = 4096, N = 57344, K = 8192: 1243 us without the overlap, 1222 with one CTA per
+            // multiprocessor, 1354 with two)
+            e = launch_dependent(widen_s8_kernel, dim3((unsigned)std::min<long long>((vr + 255) / 256, (long long)sm_count())), dim3(256),
+                                 (size_t)0, st, (const uint4*)wq + vh, (uint4*)b8 + 2 * vh, vr, 1);
+            if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "widen_s8 (overlapped) launch: %s", cudaGetErrorString(e));
+            if (int s = pair_launch(true, a8, b8, nullptr, nullptr, alpha, alpha_dev, y, M, N, K, err, st, head, tiles_n - head)) return s;
+        }
+        return WUSH_OK;
+    }
+    widen_s8_kernel<<<(unsigned)std::min<long long>((vb + 255) / 256, cap), 256, 0, st>>>((const uint4*)wq, (uint4*)b8, vb, 0);
     if (int s = check_launch("widen_s8")) return s;
-    if (use_pair_tiles(true)) return pair_launch(true, a8, b8, nullptr, nullptr, alpha, alpha_dev, y, M, N, K, err, st);
     CUtensorMap ma, mb;
     int s;
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a8, K, M, 128, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;

@@ -74,7 +74,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const PairScale sc,
-                 __half* __restrict__ y, int M, int N, int K, int gm, int* __restrict__ err)
+                 __half* __restrict__ y, int M, int N, int K, int gm, int* __restrict__ err,
+                 int tile_n_first, int tile_n_count)                 // the column tiles this launch covers
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -88,8 +89,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int tiles_m = (M + 2 * PM - 1) / (2 * PM), tiles_n = (N + PN - 1) / PN, n_tiles = tiles_m * tiles_n;
+    const int tiles_m = (M + 2 * PM - 1) / (2 * PM), tiles_n = tile_n_count, n_tiles = tiles_m * tiles_n;
     const int k_steps = K / (I8 ? 128 : 64);                         // a stage row is 128 bytes either way
+
+    pdl_launch_dependents();            // a dependent (the widening of later column tiles) may run beside this grid
 
     if (tid == 0) {
         for (int i = 0; i < P_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
@@ -116,6 +119,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int t = pair; t < n_tiles && ok; t += n_pairs) {
                 int tm, tn;
                 tile_coords(t, tiles_m, tiles_n, gm, tm, tn);
+                tn += tile_n_first;
                 const int m0 = tm * 2 * PM + (int)rank * PM, n0 = tn * PN + (int)rank * (PN / 2);
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
@@ -181,6 +185,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int t = pair; t < n_tiles && ok; t += n_pairs) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, gm, tm, tn);
+            tn += tile_n_first;
             const int m0 = tm * 2 * PM + (int)rank * PM, n0 = tn * PN;
             if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
             tc::tc_fence_after();
@@ -282,12 +287,21 @@ int pair_set_attributes()
     return WUSH_OK;
 }
 
+int pairs_resident()
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return (dev >= 0 && dev < 64 && g_pairs_resident[dev] > 0) ? g_pairs_resident[dev] : sm_count() / 2;
+}
+
 bool pair_supported(int64_t M, int64_t N, int64_t K, bool i8) { return M >= 1 && K % (i8 ? 128 : 64) == 0 && N % 8 == 0; }
 
 // a (M x K) and b (N x K): fp16 rows for the folded route, int8 rows for the per-tensor route.
+// The launch covers column tiles [tile_n_first, tile_n_first + tile_n_count) of 256 columns; a negative count means all.
 int pair_launch(bool i8, const void* a, const void* b, const float* fa, const float* fb, float alpha, const float* alpha_dev,
-                void* y, int64_t M, int64_t N, int64_t K, int* err, cudaStream_t st)
+                void* y, int64_t M, int64_t N, int64_t K, int* err, cudaStream_t st, int tile_n_first, int tile_n_count)
 {
+    if (tile_n_count < 0) { tile_n_first = 0; tile_n_count = (int)((N + PN - 1) / PN); }
     CUtensorMap ma, mb;
     int s;
     if (i8) {
@@ -300,7 +314,7 @@ int pair_launch(bool i8, const void* a, const void* b, const float* fa, const fl
     int dev = 0;
     cudaGetDevice(&dev);
     const int resident = (dev >= 0 && dev < 64 && g_pairs_resident[dev] > 0) ? g_pairs_resident[dev] : sm_count() / 2;
-    const int64_t tiles = ((M + 2 * PM - 1) / (2 * PM)) * ((N + PN - 1) / PN);
+    const int64_t tiles = ((M + 2 * PM - 1) / (2 * PM)) * tile_n_count;
     const int pairs = (int)(tiles < resident ? tiles : resident);
     const PairScale sc = {fa, fb, alpha, alpha_dev};
     // Band height: as many row blocks as keep the band's activations within about a quarter of the L2
@@ -312,9 +326,11 @@ int pair_launch(bool i8, const void* a, const void* b, const float* fa, const fl
     if (const char* v = std::getenv("WUSH_PAIR_BAND")) gm = std::max(1, atoi(v));
     if (gm > tiles_m) gm = (int)tiles_m;
     if (i8)
-        gemm_pair_kernel<true><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, gm, err);
+        gemm_pair_kernel<true><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, gm, err,
+                                                                      tile_n_first, tile_n_count);
     else
-        gemm_pair_kernel<false><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, gm, err);
+        gemm_pair_kernel<false><<<2 * pairs, P_THREADS, P_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, gm, err,
+                                                                       tile_n_first, tile_n_count);
     return check_launch("gemm_pair");
 }
 
