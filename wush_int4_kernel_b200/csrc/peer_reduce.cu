@@ -109,7 +109,7 @@ __device__ __forceinline__ void exchange_end(const PeerTable& peers, unsigned in
     }
 }
 
-// Bounded wait of warp 0 until every rank has published `target` steps; all threads get the verdict.
+// Bounded wait of warp 0 until every rank has published `target` steps; all threads get the outcome.
 __device__ __forceinline__ bool wait_all_published(const PeerTable& peers, unsigned int target)
 {
     __shared__ unsigned int s_ok2;
