@@ -394,31 +394,58 @@ def run_gpu_arm(args):
                     "frac_of_nominal_int8": tflops / INT8_NOMINAL_TOPS, "kernel": "w4a4 product", "kernel_us": kernel_ms * 1e3}
 
     # ---- end to end through the public ops: host activations in, host result out -------------
+    # Requests arrive in pinned host memory and their results return there.  Consecutive requests are
+    # independent, so the public helper host_pipeline.HostStreamedLayer overlaps the upload of request i + 1 and
+    # the download of request i - 1 with the kernels of request i (three streams, double-buffered device
+    # tensors); every request makes its own host -> device -> host trip inside the timed region.  A block of
+    # E2E_BLOCK requests is one CUDA Graph; args.steps requests are timed exactly (whole blocks + a remainder).
+    from wush_int4_kernel_b200.host_pipeline import HostStreamedLayer
+    E2E_BLOCK = 16
     x_host = [synth.draw_activations(M, K_DIM, outliers, gen).cpu().pin_memory() for _ in range(4)]
-    y_host = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
+    y_host = [torch.empty(M, n_local, dtype=torch.float16).pin_memory() for _ in range(E2E_BLOCK)]
+    pipe = HostStreamedLayer(t_bf16, M)
+
+    def e2e_block(first, count):
+        pipe.run([x_host[(first + k) % 4] for k in range(count)], y_host[:count],
+                 [weights[(first + k) % copies] for k in range(count)])
+
+    # block b starts at request b * E2E_BLOCK; inputs repeat with period 4 and weights with period `copies`
+    period = (4 * copies // math.gcd(4, copies))
+    block_period = period // math.gcd(period, E2E_BLOCK)
+    e2e_graphs = [timing.capture(lambda b=b: e2e_block(b * E2E_BLOCK, E2E_BLOCK))[0] for b in range(block_period)]
+    whole, rest = divmod(args.steps, E2E_BLOCK)
+    rest_graph = timing.capture(lambda: e2e_block(whole * E2E_BLOCK, rest))[0] if rest else None
+
+    # the same request handled alone (upload -> kernels -> download, nothing overlapped): its latency
     x_dev = torch.empty(M, K_DIM, dtype=torch.bfloat16, device=dev)
+    y_one = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
 
-    def e2e_step(i):
+    def e2e_single(i):
         x_dev.copy_(x_host[i % 4], non_blocking=True)
-        wq, ws = weights[i % copies]
         a, b = quantise_activations(x_dev, t_bf16)
-        y_host.copy_(w4a4_product(a, b, wq, ws), non_blocking=True)
+        y_one.copy_(w4a4_product(a, b, *weights[i % copies]), non_blocking=True)
 
-    # The same step as the user-facing replay form: pinned-host -> device copy, the two kernels and
-    # the device -> pinned-host copy captured into one CUDA Graph per (input buffer, weight copy).
-    period = 4 * copies // math.gcd(4, copies)
-    e2e_graphs = [timing.capture(lambda i=i: e2e_step(i))[0] for i in range(period)]
+    single_graphs = [timing.capture(lambda i=i: e2e_single(i))[0] for i in range(period)]
+    for i in range(8):
+        single_graphs[i % period].replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(64):
+        single_graphs[i % period].replay()
+    e1.record()
+    torch.cuda.synchronize()
+    latency_us = 1e3 * e0.elapsed_time(e1) / 64
 
-    def e2e_replay(i):
-        e2e_graphs[i % period].replay()
-
-    for i in range(max(args.warmup, 3)):
-        e2e_replay(i)
+    for b in range(max(1, -(-max(args.warmup, 3) // E2E_BLOCK))):
+        e2e_graphs[b % block_period].replay()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        e2e_replay(i)
+    for b in range(whole):
+        e2e_graphs[b % block_period].replay()
+    if rest_graph is not None:
+        rest_graph.replay()
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -426,16 +453,22 @@ def run_gpu_arm(args):
         tmax = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         e2e_ms = float(tmax.item())
-    # the host buffer of the last replay must hold the product of its inputs
+    # the host buffers of the last replay must hold the products of their inputs
     torch.cuda.synchronize()
-    last = args.steps - 1
-    a, b = quantise_activations(x_host[last % 4].to(dev), t_bf16)
-    expect = w4a4_product(a, b, *weights[last % copies]).cpu()
-    e2e_check = bool(torch.equal(expect, y_host))
+    last_first, last_count = (whole * E2E_BLOCK, rest) if rest else ((whole - 1) * E2E_BLOCK, E2E_BLOCK)
+    e2e_check = True
+    for k in range(last_count):
+        a, b = quantise_activations(x_host[(last_first + k) % 4].to(dev), t_bf16)
+        expect = w4a4_product(a, b, *weights[(last_first + k) % copies]).cpu()
+        e2e_check = e2e_check and bool(torch.equal(expect, y_host[k]))
     e2e_tops = 2.0 * M * N_DIM * K_DIM / (e2e_ms / args.steps * 1e-3) / 1e12
     e2e = {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": 2 * M * K_DIM * world,
            "d2h_bytes_per_step": 2 * M * N_DIM, "us_per_step": 1e3 * e2e_ms / args.steps,
-           "form": "CUDA Graph of pinned H2D copy -> transform+quant -> product -> pinned D2H copy"}
+           "latency_us_one_request_alone": latency_us,
+           "form": f"requests in pinned host memory; per request: H2D copy -> transform+quant -> product -> D2H copy; "
+                   f"{E2E_BLOCK} requests per CUDA Graph on three streams (upload of the next and download of the previous "
+                   f"request overlap the kernels of the current one: host_pipeline.HostStreamedLayer); "
+                   f"`latency_us_one_request_alone` is the same chain with nothing overlapped"}
 
     # ---- the other half of the metric in the same run: M = 4096 through the same layer --------
     prefill = None
@@ -445,7 +478,7 @@ def run_gpu_arm(args):
     # ---- tensor-parallel FFN block with its exchange (N > 1) -----------------------------------
     ffn_block = None
     if world > 1 and not args.no_ffn:
-        del graphs, prod_graphs, e2e_graphs
+        del graphs, prod_graphs, e2e_graphs, single_graphs, rest_graph
         ffn_block = measure_ffn_block(world, rank, dev)
 
     if rank != 0:

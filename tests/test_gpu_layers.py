@@ -369,3 +369,37 @@ def test_peer_allreduce_two_phase_single_rank_and_sequential_ranks():
     finally:
         for c in comms:
             capi.check(lib.wush_comm_destroy(c), "comm_destroy")
+
+
+@pytest.mark.parametrize("rows", [1, 8])
+def test_host_streamed_layer_equals_plain_layer(setup, rows):
+    """Requests from pinned host memory through the three-stream pipeline (uploads, kernels and downloads of
+    consecutive requests overlap): every result equals the plain layer's, eagerly and replayed from one graph,
+    with more requests than device buffers and alternating weights."""
+    from wush_int4_kernel_b200.host_pipeline import HostStreamedLayer
+    from wush_int4_kernel_b200.linear import W4A4Linear
+    _C, synth, layer, gen = setup
+    other = synth.make_layer(1024, 768, seed=11, device="cuda", quantiser=_C.quant_int4)
+    weights = [(layer.wq, layer.ws), (other.wq, other.ws)]
+    xs = [synth.draw_activations(rows, 1024, layer.outliers, gen) for _ in range(7)]
+    want = [W4A4Linear(layer.t_bf16, *weights[i % 2])(x).cpu() for i, x in enumerate(xs)]
+    x_hosts = [x.cpu().pin_memory() for x in xs]
+    y_hosts = [torch.zeros(rows, 768, dtype=torch.float16).pin_memory() for _ in xs]
+    pipe = HostStreamedLayer(layer.t_bf16, rows)
+    pipe.run(x_hosts, y_hosts, weights)
+    torch.cuda.synchronize()
+    for i, (y, w) in enumerate(zip(y_hosts, want)):
+        assert torch.equal(y, w), f"eager, request {i}"
+    for y in y_hosts:
+        y.zero_()
+    from wush_int4_kernel_b200 import timing
+    graph, _ = timing.capture(lambda: pipe.run(x_hosts, y_hosts, weights))
+    for y in y_hosts:
+        y.zero_()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for i, (y, w) in enumerate(zip(y_hosts, want)):
+        assert torch.equal(y, w), f"graph, request {i}"
+    with pytest.raises(ValueError):
+        pipe.run([xs[0].cpu()], [y_hosts[0]], weights)          # not pinned
