@@ -41,6 +41,11 @@ def _worker(rank, world, port, ret):
         local = orc.gemm_f16(xq, xs, layer.wq[n0:n1].numpy(), orc.bits(layer.ws[n0:n1]))
         y = gather_columns(orc.from_bits(local, torch.float16), bounds)
         ok_col = np.array_equal(orc.bits(y), full)
+        # equal shards (the first 256 columns as 2 + 2 units of 64): the gather without the padding pass
+        eq_bounds = [shard_bounds(256, world, r, 64) for r in range(world)]
+        e0, e1 = eq_bounds[rank]
+        y_eq = gather_columns(orc.from_bits(full[:, e0:e1].copy(), torch.float16), eq_bounds)
+        ok_col = ok_col and np.array_equal(orc.bits(y_eq), full[:, :256])
 
         # row parallel: K split on whole groups, partial products summed in fp32
         k0, k1 = shard_bounds(K, world, rank, 32)
