@@ -241,12 +241,34 @@ def test_pair_tile_kernel_equals_single_cta_kernel(dev, orc, shape, monkeypatch)
     ops = _operands(M, N, K, seed=M + N, orc=orc)
     y64 = orc.gemm_f64(*ops)
     dops = _to_dev(dev, *ops)
+    monkeypatch.setenv("WUSH_TAIL_SPLIT", "0")        # the single-CTA kernel otherwise sums the last wave's tiles in K ranges
     monkeypatch.setenv("WUSH_TILE_KERNEL", "pair")
     y_pair = cabi.gemm(*dops, variant=capi.GEMM_TILE_F16)
     monkeypatch.setenv("WUSH_TILE_KERNEL", "single")
     y_single = cabi.gemm(*dops, variant=capi.GEMM_TILE_F16)
     _assert_close(y_pair, y64, shape)
     assert torch.equal(y_pair, y_single)
+
+
+@pytest.mark.parametrize("shape", [(2100, 264, 512), (2304, 2048, 1024), (4096, 1536, 2048), (2100, 9472, 256)])
+def test_last_wave_in_k_ranges(dev, orc, shape, monkeypatch):
+    """The tiles of the last, partly filled wave of the pre-widened route are cut into K ranges that run side by
+    side and are summed afterwards (18, 72, 96 and 333 = 2 x 148 + 37 tiles here).  Against the fp64 arbiter, and
+    against the same product without the cut: the operands' products are exact in fp32, only the order of the
+    additions differs."""
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=M + K, orc=orc)
+    dops = _to_dev(dev, *ops)
+    monkeypatch.setenv("WUSH_TILE_KERNEL", "single")
+    monkeypatch.setenv("WUSH_TAIL_SPLIT", "1")
+    y_cut = cabi.gemm(*dops, variant=capi.GEMM_TILE_F16)
+    monkeypatch.setenv("WUSH_TAIL_SPLIT", "0")
+    y_whole = cabi.gemm(*dops, variant=capi.GEMM_TILE_F16)
+    if M * N * K <= 2100 * 2048 * 1024:
+        _assert_close(y_cut, orc.gemm_f64(*ops), shape)
+    d = (y_cut.float() - y_whole.float()).abs()
+    assert float(d.max()) <= 2e-3 * float(y_whole.float().abs().max())
+    assert float((d > 0).float().mean()) < 0.2
 
 
 def test_decode_tcgen05_exact_group_sums(dev, orc):

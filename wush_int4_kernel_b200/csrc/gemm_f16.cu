@@ -643,7 +643,8 @@ template <bool I8>
 __global__ void __launch_bounds__(T_THREADS, 1)
 gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TileScale sc,
                       __half* __restrict__ y, int M, int N, int K, int* __restrict__ err,
-                      int tile_n_first, int tile_n_count)                     // the column tiles this launch covers
+                      int tile_n_first, int tile_n_count,                     // the column tiles this launch covers
+                      int full_tiles, int tail_split, float* __restrict__ part) // tiles taken whole; K ranges of the others
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -657,6 +658,11 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_m = (M + 2 * FM - 1) / (2 * FM), n_tiles = tiles_m * tile_n_count;
     const int k_steps = K / (I8 ? 128 : 64);                 // a stage row is 128 bytes either way
+    // Units of work: the first `full_tiles` tiles (whole waves of the grid) run over the whole K; each of the
+    // remaining tiles -- the last, partly filled wave -- is cut into `tail_split` K ranges that run side by side,
+    // leave their fp32 accumulators in `part` and are summed by tail_sum_kernel.
+    const int n_units = full_tiles + (n_tiles - full_tiles) * tail_split;
+    const int tail_steps = k_steps / tail_split;
 
     // A dependent launched behind this grid (the widening of the next column tiles) may start as soon as
     // every CTA is resident: it runs in the threads and registers this kernel leaves free.
@@ -683,9 +689,12 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint32_t slot = 0, phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / tail_split;
+                const int ks_first = u < full_tiles ? 0 : ((u - full_tiles) % tail_split) * tail_steps;
+                const int ks_end = u < full_tiles ? k_steps : ks_first + tail_steps;
                 const int m0 = (t % tiles_m) * 2 * FM, n0 = (tile_n_first + t / tiles_m) * FN;
-                for (int ks = 0; ks < k_steps; ++ks) {
+                for (int ks = ks_first; ks < ks_end; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
                     uint8_t* st = smem + slot * T_STAGE;
                     tc::mbar_expect_tx(&full[slot], T_STAGE);
@@ -707,10 +716,11 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint32_t slot = 0, phase = 0, aphase = 0;
             const uint32_t idesc = I8 ? tc::idesc_i8(FN) : tc::idesc_f16(FN);
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int unit_steps = u < full_tiles ? k_steps : tail_steps;
                 if (!tc::mbar_wait(acc_empty, aphase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after();
-                for (int ks = 0; ks < k_steps; ++ks) {
+                for (int ks = 0; ks < unit_steps; ++ks) {
                     if (!tc::mbar_wait(&full[slot], phase)) { ok = false; break; }
                     tc::tc_fence_after();
                     const uint32_t sa = tc::smem_u32(smem + slot * T_STAGE), sb = sa + TA_BYTES;
@@ -743,8 +753,11 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         uint32_t aphase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / tail_split;
             const int m0 = (t % tiles_m) * 2 * FM, n0 = (tile_n_first + t / tiles_m) * FN;
+            // a K range of a tail tile: raw fp32 (int32) accumulators, 256 x 256 per unit, row-major
+            float* prow = u < full_tiles ? nullptr : part + ((size_t)(u - full_tiles) * (2 * FM) + row) * FN;
             if (!tc::mbar_wait(acc_full, aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -762,7 +775,12 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     if (lane == 0) tc::mbar_arrive(acc_empty);
                 }
                 const int n = n0 + c * 32;
-                if (m < M && n < N) {
+                if (prow) {                                     // 128 bytes per lane: four 32-byte stores
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        st_global_v8(prow + c * 32 + q * 8, make_uint4(v[q * 8], v[q * 8 + 1], v[q * 8 + 2], v[q * 8 + 3]),
+                                     make_uint4(v[q * 8 + 4], v[q * 8 + 5], v[q * 8 + 6], v[q * 8 + 7]));
+                } else if (m < M && n < N) {
                     __half* yr = y + (size_t)m * N + n;
                     const bool wide = ((reinterpret_cast<uintptr_t>(y) & 31) == 0) && (N & 15) == 0;   // 32-byte stores possible
                     uint4 prev = make_uint4(0, 0, 0, 0);
@@ -804,6 +822,56 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     tc::tc_fence_before();
     __syncthreads();
     if (warp == 1) tc::tmem_dealloc(tmem, 512);
+}
+
+// Sum of the K ranges of the tail tiles (in order: deterministic), scaled and rounded to fp16 once.  One thread per
+// 8 consecutive outputs of a row of a 256 x 256 tile; `part` as written by the tile kernel.
+template <bool I8>
+__global__ void __launch_bounds__(256)
+tail_sum_kernel(const float* __restrict__ part, const TileScale sc, __half* __restrict__ y, int M, int N, int tiles_m,
+                int tile_n_first, int full_tiles, int tail_split)
+{
+    const int tt = blockIdx.y;                                          // tail tile
+    const int e = blockIdx.x * 256 + threadIdx.x;                       // 8-output vector inside the tile
+    const int row = e >> 5, col = (e & 31) * 8;
+    const int t = full_tiles + tt;
+    const int m = (t % tiles_m) * 2 * FM + row, n = (tile_n_first + t / tiles_m) * FN + col;
+    if (m >= M || n + 8 > N) return;
+    const float* p = part + ((size_t)tt * tail_split * (2 * FM) + row) * FN + col;
+    float acc[8];
+    int iacc[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { acc[q] = 0.f; iacc[q] = 0; }
+    for (int r = 0; r < tail_split; ++r) {
+        const float4 a = *reinterpret_cast<const float4*>(p + (size_t)r * (2 * FM) * FN);
+        const float4 b = *reinterpret_cast<const float4*>(p + (size_t)r * (2 * FM) * FN + 4);
+        const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if constexpr (I8) iacc[q] += __float_as_int(f[q]);
+            else acc[q] += f[q];
+        }
+    }
+    float fs[8];
+    float fm;
+    if constexpr (I8) {
+        fm = sc.alpha_dev ? __ldg(sc.alpha_dev) : sc.alpha;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { acc[q] = (float)iacc[q]; fs[q] = 1.f; }
+    } else {
+        fm = sc.fa[m];
+        const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n), f1 = *reinterpret_cast<const float4*>(sc.fb + n + 4);
+        fs[0] = f0.x; fs[1] = f0.y; fs[2] = f0.z; fs[3] = f0.w; fs[4] = f1.x; fs[5] = f1.y; fs[6] = f1.z; fs[7] = f1.w;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        __half2 h;
+        if constexpr (I8) h = __floats2half2_rn(__fmul_rn(fm, acc[2 * q]), __fmul_rn(fm, acc[2 * q + 1]));
+        else h = __floats2half2_rn(acc[2 * q] * (fm * fs[2 * q]), acc[2 * q + 1] * (fm * fs[2 * q + 1]));
+        o[q] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)m * N + n) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
@@ -904,8 +972,13 @@ static bool f16_takes_fused(int64_t M, int64_t N, int64_t K, const void* ws) { r
 // (for a 16-byte-aligned `ws`, which is what wush_w4a4_gemm_workspace_bytes assumes).
 size_t f16_workspace_bytes_min(int64_t M, int64_t N, int64_t K) { return f16_layout_bytes(M, N, K, use_fused(M, N, K)); }
 
+// Room for the fp32 accumulators of the K ranges into which the pre-widened route cuts the tiles of its last,
+// partly filled wave (at most one 256 x 256 tile per multiprocessor).
+static size_t tail_part_bytes() { return (size_t)sm_count() * (2 * FM) * FN * 4; }
+
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
+    if (!use_fused(M, N, K)) return f16_workspace_bytes_min(M, N, K) + tail_part_bytes() + 256;
     const int split = f16_fused_split(M, N, K);
     return f16_workspace_bytes_min(M, N, K) + (split > 1 ? align256((size_t)split * M * N * 4) : 0);
 }
@@ -953,6 +1026,44 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
         gemm_f16_fused_kernel<<<grid, Q_THREADS, Q_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N,
                                                                 (int)K, err);
     return check_launch("gemm_f16_fused");
+}
+
+// The last wave of a persistent tile grid is rarely full (M = 4096, K = 8192: 3584 tiles are 24.2 waves of 148; a
+// shard of 7168 columns 3.03).  Its tiles are cut into K ranges -- a power of two that divides the K steps,
+// leaves ranges of at least 4 steps and makes no more units than there are multiprocessors -- which run side by
+// side; tail_sum_kernel adds them.  {tiles taken whole, ranges per remaining tile}; {tiles, 1} = no cut.
+struct TailPlan { int full_tiles, split; };
+static TailPlan plan_tail(int64_t tiles, int k_steps, bool room)
+{
+    TailPlan p = {(int)tiles, 1};
+    const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0 switches the cut off (measurements, A/B tests)
+    if (!room || (v && v[0] == '0')) return p;
+    const int sms = sm_count();
+    const int full = (int)(tiles / sms) * sms, tail = (int)tiles - full;
+    if (tail == 0) return p;
+    int r = 1;
+    while (tail * r * 2 <= sms && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4) r *= 2;
+    if (r > 1) { p.full_tiles = full; p.split = r; }
+    return p;
+}
+
+template <bool I8>
+static int launch_tile2(const CUtensorMap& ma, const CUtensorMap& mb, const TileScale& sc, void* y, int64_t M, int64_t N, int64_t K,
+                        int* err, int tile_n_first, int tile_n_count, float* part, cudaStream_t st)
+{
+    const int tiles_m = (int)((M + 2 * FM - 1) / (2 * FM));
+    const int64_t tiles = (int64_t)tiles_m * tile_n_count;
+    const TailPlan tp = plan_tail(tiles, (int)(K / (I8 ? 128 : 64)), part != nullptr);
+    const int64_t units = tp.full_tiles + (tiles - tp.full_tiles) * tp.split;
+    gemm_tile2_kernel<I8><<<(int)std::min<int64_t>(units, sm_count()), T_THREADS, T_TOTAL, st>>>(
+        ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, tile_n_first, tile_n_count, tp.full_tiles, tp.split, part);
+    if (int s = check_launch("gemm_tile2")) return s;
+    if (tp.split > 1) {
+        const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - tp.full_tiles));
+        tail_sum_kernel<I8><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, tiles_m, tile_n_first, tp.full_tiles, tp.split);
+        return check_launch("tail_sum");
+    }
+    return WUSH_OK;
 }
 
 // `sticky_err`: where the kernels record a bounded wait that gave up.  Null = word 0 of the scratch, cleared
@@ -1012,10 +1123,13 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, K, M, 64, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b16, K, N, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     const TileScale sc = {fa, fb, 0.f, nullptr};
-    const int64_t tiles_head = (int64_t)tiles_m * head;
-    gemm_tile2_kernel<false><<<(int)std::min<int64_t>(tiles_head, sm_count()), T_THREADS, T_TOTAL, st>>>(
-        ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, 0, head);
-    if ((s = check_launch("gemm_f16"))) return s;
+    // the K ranges of the last wave's tiles need room behind the layout of this route
+    // (the tile kernel writes them with 32-byte stores: the area starts on the next 256-byte boundary of the ADDRESS,
+    // whatever the alignment of the scratch itself)
+    const uintptr_t part_addr = (reinterpret_cast<uintptr_t>(base) + f16_layout_bytes(M, N, K, false) + 255) & ~uintptr_t(255);
+    float* part = part_addr + tail_part_bytes() <= reinterpret_cast<uintptr_t>(base) + workspace_bytes
+                      ? reinterpret_cast<float*>(part_addr) : nullptr;
+    if ((s = launch_tile2<false>(ma, mb, sc, y, M, N, K, err, 0, head, head < tiles_n ? nullptr : part, st))) return s;
     if (head < tiles_n) {
         const long long rest = N - head_rows;
         // One CTA of 8 warps per multiprocessor, all resident beside the GEMM (measured, whole product in us at
@@ -1027,10 +1141,7 @@ int f16_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const voi
                                          wq + (size_t)head_rows * (K / 2), ws16 + (size_t)head_rows * (K / 32),
                                          b16 + (size_t)head_rows * K, fb + head_rows, rest, (int)K);
         if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "dequant_f16 (overlapped) launch: %s", cudaGetErrorString(e));
-        const int64_t tiles_rest = (int64_t)tiles_m * (tiles_n - head);
-        gemm_tile2_kernel<false><<<(int)std::min<int64_t>(tiles_rest, sm_count()), T_THREADS, T_TOTAL, st>>>(
-            ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, head, tiles_n - head);
-        if ((s = check_launch("gemm_f16"))) return s;
+        if ((s = launch_tile2<false>(ma, mb, sc, y, M, N, K, err, head, tiles_n - head, part, st))) return s;
     }
     return WUSH_OK;
 }
@@ -1130,12 +1241,8 @@ int i8_tile_dispatch(const uint8_t* xq, const uint8_t* wq, int64_t M, int64_t N,
     int s;
     if ((s = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a8, K, M, 128, 2 * FM, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
     if ((s = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b8, K, N, 128, FN, CU_TENSOR_MAP_SWIZZLE_128B))) return s;
-    const int64_t tiles = ((M + 2 * FM - 1) / (2 * FM)) * ((N + FN - 1) / FN);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const TileScale sc = {nullptr, nullptr, alpha, alpha_dev};
-    gemm_tile2_kernel<true><<<grid, T_THREADS, T_TOTAL, st>>>(ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, 0,
-                                                              (int)((N + FN - 1) / FN));
-    return check_launch("gemm_i8_tile");
+    return launch_tile2<true>(ma, mb, sc, y, M, N, K, err, 0, (int)((N + FN - 1) / FN), nullptr, st);
 }
 
 }  // namespace wush
