@@ -150,9 +150,10 @@ int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq, const v
  * themselves once they are running: servers that size a single arena at start-up and forbid
  * cudaMalloc afterwards, processes held to a fixed device-memory budget, control loops that
  * cannot tolerate the implicit synchronisation of an allocation.  Same arithmetic as
- * wush_w4a4_gemm(..., WUSH_GEMM_TILE_F16, ...) (bit-identical to it wherever that call does not
- * split K over several work units, i.e. on all but narrow layers; within the same 1e-3 of the
- * fp64 result everywhere), but the scratch is an array of WUSH_STATIC_SCRATCH_BYTES that is part
+ * wush_w4a4_gemm(..., WUSH_GEMM_TILE_F16, ...): that call, given the scratch its size query asks
+ * for, cuts the tiles of a partly filled wave into K ranges and adds them afterwards, which this
+ * entry point has no room for -- same products, another order of the fp32 additions; both are
+ * within the same 1e-3 of the fp64 result, and bit-identical where no tile is cut.  The scratch is an array of WUSH_STATIC_SCRATCH_BYTES that is part
  * of the library image: every GPU that loads the library keeps it until the process exits, so
  * the limit is deliberately modest.
  *   - Scratch needed: about 2*M*K bytes when the weights are widened inside the GEMM (M <= 2048,

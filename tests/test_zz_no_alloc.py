@@ -30,8 +30,11 @@ def _operands(M, N, K, seed, dev):
     return (to(xq), to(xs, torch.bfloat16), to(wq), to(ws, torch.bfloat16)), orc.gemm_f64(xq, xs, wq, ws)
 
 
-def test_static_scratch_entry_point_two_calls_in_a_row():
+def test_static_scratch_entry_point_two_calls_in_a_row(monkeypatch):
     assert torch.cuda.is_available(), "needs a CUDA device"
+    # with room behind its scratch the caller-scratch entry point cuts tiles into K ranges; the built-in array has
+    # no such room, so for the bit-for-bit comparison below the cut is switched off
+    monkeypatch.setenv("WUSH_TAIL_SPLIT", "0")
     from tests import cabi
     from wush_int4_kernel_b200 import capi
 
@@ -49,7 +52,7 @@ def test_static_scratch_entry_point_two_calls_in_a_row():
     #   (300, 520, 1024)  weights widened inside the GEMM, 256-row tiles
     #   (130, 264, 320)   K % 256 != 0: the route with an fp16 copy of the weights in the array
     #   (130, 264, 512)   weights widened inside the GEMM again
-    # On these shapes the caller-scratch call does not split K, so the two must agree bit for bit.
+    # Without K ranges in the caller-scratch call the two must agree bit for bit.
     for seed, (M, N, K) in enumerate([(300, 520, 1024), (130, 264, 320), (130, 264, 512)]):
         (xq, xs, wq, ws), y64 = _operands(M, N, K, 100 + seed, dev)
         expect = cabi.gemm(xq, xs, wq, ws, variant=capi.GEMM_TILE_F16)         # caller-provided scratch

@@ -413,13 +413,15 @@ constexpr int R_BARS = R_BOFF + R_BUFS * QB_BYTES;
 constexpr int R_TOTAL = R_BARS + (2 * R_STAGES + 2 * R_BUFS + 2 * F_ACC + 1) * 8 + 16 + 1024;
 
 //
-// Split K (ksplit > 1, few tiles on many multiprocessors): the unit of work is (tile, K range); a unit's
-// scaled fp32 results go to part[range][M][N] instead of y and splitk_reduce_kernel adds the ranges in
-// order.  A range is a whole number of 16-byte scale vectors (4 stages).
+// Units of work: the first `full_tiles` tiles run over the whole K and write y; every other tile is cut into
+// `ksplit` K ranges (few tiles on many multiprocessors: all tiles, full_tiles = 0; many tiles: only those of the
+// last, partly filled wave).  A range leaves its raw fp32 accumulators in part[unit - full_tiles][256][256] and
+// tail_sum_kernel adds the ranges of a tile in order.  A range is a whole number of 16-byte scale vectors
+// (4 stages).
 __global__ void __launch_bounds__(R_THREADS, 1)
 gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
                       const unsigned short* __restrict__ ws, const float* __restrict__ down, const TileScale sc,
-                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err, int ksplit,
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err, int full_tiles, int ksplit,
                       float* __restrict__ part)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -434,8 +436,9 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN, n_units = tiles_m * tiles_n * ksplit;
-    const int k_steps = K / 64 / ksplit, G = K >> 5;               // stages per unit
+    const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN;
+    const int n_units = full_tiles + (tiles_m * tiles_n - full_tiles) * ksplit;
+    const int all_steps = K / 64, range_steps = all_steps / ksplit, G = K >> 5;     // stages of a whole tile / of a K range
 
     if (tid == 0) {
         for (int i = 0; i < R_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 17); }
@@ -460,7 +463,9 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int issued = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-                const int t = u / ksplit, ks0 = (u % ksplit) * k_steps;
+                const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / ksplit;
+                const int ks0 = u < full_tiles ? 0 : ((u - full_tiles) % ksplit) * range_steps;
+                const int k_steps = u < full_tiles ? all_steps : range_steps;
                 const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
                 for (int ks = ks0; ks < ks0 + k_steps; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
@@ -485,6 +490,7 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t idesc = tc::idesc_f16(FN);
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int k_steps = u < full_tiles ? all_steps : range_steps;
                 if (!tc::mbar_wait(&acc_empty[0], aphase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
@@ -517,7 +523,9 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t slot = 0, phase = 0, buf = 0, bphase = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const int t = u / ksplit, ks0 = (u % ksplit) * k_steps, ks1 = ks0 + k_steps;   // ks0 is a multiple of 4
+            const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / ksplit;
+            const int ks0 = u < full_tiles ? 0 : ((u - full_tiles) % ksplit) * range_steps;        // a multiple of 4
+            const int ks1 = ks0 + (u < full_tiles ? all_steps : range_steps);
             const int n = (t / tiles_m) * FN + d;
             const bool live = n < N;
             const float dn = live ? down[n] : 0.f;
@@ -561,9 +569,9 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t aphase = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const int t = u / ksplit;
+            const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / ksplit;
             const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
-            float* prow = part + ((size_t)(u % ksplit) * M + (m0 + row < M ? m0 + row : 0)) * N;   // ksplit > 1 only
+            float* prow = u < full_tiles ? nullptr : part + ((size_t)(u - full_tiles) * (2 * FM) + row) * FN;
             if (!tc::mbar_wait(&acc_full[0], aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -579,7 +587,12 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     if (lane == 0) tc::mbar_arrive(&acc_empty[0]);
                 }
                 const int n = n0 + c * 32;
-                if (m < M && n < N) {
+                if (prow) {                                     // 128 bytes per lane: four 32-byte stores
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        st_global_v8(prow + c * 32 + q * 8, make_uint4(v[q * 8], v[q * 8 + 1], v[q * 8 + 2], v[q * 8 + 3]),
+                                     make_uint4(v[q * 8 + 4], v[q * 8 + 5], v[q * 8 + 6], v[q * 8 + 7]));
+                } else if (m < M && n < N) {
                     __half* yr = y + (size_t)m * N + n;
                     const bool wide = ((reinterpret_cast<uintptr_t>(y) & 31) == 0) && (N & 15) == 0;   // 32-byte stores possible
                     uint4 prev = make_uint4(0, 0, 0, 0);
@@ -589,15 +602,6 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             const float4 f0 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8);
                             const float4 f1 = *reinterpret_cast<const float4*>(sc.fb + n + v8 * 8 + 4);
                             const float fs[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-                            if (ksplit > 1) {
-                                float r[8];
-#pragma unroll
-                                for (int p = 0; p < 8; ++p) r[p] = __uint_as_float(v[v8 * 8 + p]) * (fm * fs[p]);
-                                float4* dst = reinterpret_cast<float4*>(prow + n + v8 * 8);
-                                dst[0] = make_float4(r[0], r[1], r[2], r[3]);
-                                dst[1] = make_float4(r[4], r[5], r[6], r[7]);
-                                continue;
-                            }
                             uint32_t o[4];
 #pragma unroll
                             for (int p = 0; p < 4; ++p) {
@@ -876,24 +880,6 @@ tail_sum_kernel(const float* __restrict__ part, const TileScale sc, __half* __re
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
-// y = fp16(sum over the K ranges, in order, of the fp32 partial results); 8 outputs per thread
-__global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float4* __restrict__ part, uint4* __restrict__ y, long long n_vec, int ksplit)
-{
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_vec) return;
-    float4 a = part[2 * i], b = part[2 * i + 1];
-    for (int s = 1; s < ksplit; ++s) {
-        const float4 c = part[2 * (s * n_vec + i)], d = part[2 * (s * n_vec + i) + 1];
-        a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
-        b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
-    }
-    const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
-    const __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
-    y[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
-                      *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
-}
-
 }  // namespace
 
 int pair_set_attributes();
@@ -978,9 +964,29 @@ static size_t tail_part_bytes() { return (size_t)sm_count() * (2 * FM) * FN * 4;
 
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
-    if (!use_fused(M, N, K)) return f16_workspace_bytes_min(M, N, K) + tail_part_bytes() + 256;
-    const int split = f16_fused_split(M, N, K);
-    return f16_workspace_bytes_min(M, N, K) + (split > 1 ? align256((size_t)split * M * N * 4) : 0);
+    // K ranges exist on the pre-widened route, on the 256-row kernel with in-kernel widening (M > 128) and where few
+    // tiles are cut into ranges as a whole; their accumulators live behind the layout, on a 256-byte boundary
+    if (!use_fused(M, N, K) || M > FM || f16_fused_split(M, N, K) > 1) return f16_workspace_bytes_min(M, N, K) + tail_part_bytes() + 256;
+    return f16_workspace_bytes_min(M, N, K);
+}
+
+// The last wave of a persistent tile grid is rarely full (M = 4096, K = 8192: 3584 tiles are 24.2 waves of 148; a
+// shard of 7168 columns 3.03).  Its tiles are cut into K ranges -- a power of two that divides the K steps,
+// leaves ranges of at least 4 steps and makes no more units than there are multiprocessors -- which run side by
+// side; tail_sum_kernel adds them.  {tiles taken whole, ranges per remaining tile}; {tiles, 1} = no cut.
+struct TailPlan { int full_tiles, split; };
+static TailPlan plan_tail(int64_t tiles, int k_steps, bool room, int step_multiple = 1)
+{
+    TailPlan p = {(int)tiles, 1};
+    const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0 switches the cut off (measurements, A/B tests)
+    if (!room || (v && v[0] == '0')) return p;
+    const int sms = sm_count();
+    const int full = (int)(tiles / sms) * sms, tail = (int)tiles - full;
+    if (tail == 0) return p;
+    int r = 1;
+    while (tail * r * 2 <= sms && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4 && (k_steps / (r * 2)) % step_multiple == 0) r *= 2;
+    if (r > 1) { p.full_tiles = full; p.split = r; }
+    return p;
 }
 
 static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N,
@@ -992,9 +998,12 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     float* fa = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a16) + align256((size_t)M * K * 2));
     float* fb = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fa) + align256((size_t)M * 4));
     float* dn = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fb) + align256((size_t)N * 4));
-    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(dn) + align256((size_t)N * 4));
+    // accumulators of K ranges: behind the layout, on the next 256-byte boundary of the address (32-byte stores)
+    const uintptr_t part_addr = (reinterpret_cast<uintptr_t>(dn) + align256((size_t)N * 4) + 255) & ~uintptr_t(255);
+    const bool part_room = part_addr + tail_part_bytes() <= reinterpret_cast<uintptr_t>(base) + workspace_bytes;
+    float* part = part_room ? reinterpret_cast<float*>(part_addr) : nullptr;
     int split = f16_fused_split(M, N, K);
-    if (workspace_bytes < f16_workspace_bytes(M, N, K) || !aligned16(y)) split = 1;   // scratch without room for the partial results
+    if (!part_room || !aligned16(y)) split = 1;                          // scratch without room for the partial results
     if (!sticky_err) {
         cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), st);
         if (e != cudaSuccess) return fail(WUSH_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
@@ -1009,42 +1018,26 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     if ((s = make_map_2d(&mp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K / 2, N, 32, FN, CU_TENSOR_MAP_SWIZZLE_NONE))) return s;
     const int tile_rows = wide ? 2 * FM : FM;
     const int64_t tiles = ((M + tile_rows - 1) / tile_rows) * ((N + FN - 1) / FN);
-    const int64_t units = wide ? tiles * split : tiles;
-    const int grid = (int)(units < sm_count() ? units : sm_count());
     const TileScale sc = {fa, fb, 0.f, nullptr};
     if (wide) {
-        gemm_f16_fused2_kernel<<<grid, R_THREADS, R_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M,
-                                                                 (int)N, (int)K, err, split, part);
-        if (split > 1) {
-            if (int s2 = check_launch("gemm_f16_fused")) return s2;
-            const long long n_vec = (long long)M * N / 8;
-            splitk_reduce_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float4*>(part),
-                                                                                reinterpret_cast<uint4*>(y), n_vec, split);
-            return check_launch("splitk_reduce");
+        // few tiles: every tile in `split` K ranges; many tiles: only those of the last, partly filled wave
+        TailPlan tp = {0, split};
+        if (split == 1) tp = plan_tail(tiles, (int)(K / 64), part_room && aligned16(y), 4);
+        const int64_t units = tp.full_tiles + (tiles - tp.full_tiles) * tp.split;
+        gemm_f16_fused2_kernel<<<(int)std::min<int64_t>(units, sm_count()), R_THREADS, R_TOTAL, st>>>(
+            ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N, (int)K, err, tp.full_tiles, tp.split, part);
+        if (int s2 = check_launch("gemm_f16_fused")) return s2;
+        if (tp.split > 1) {
+            const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - tp.full_tiles));
+            tail_sum_kernel<false><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, (int)((M + 2 * FM - 1) / (2 * FM)), 0,
+                                                        tp.full_tiles, tp.split);
+            return check_launch("tail_sum");
         }
-    } else
-        gemm_f16_fused_kernel<<<grid, Q_THREADS, Q_TOTAL, st>>>(ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N,
-                                                                (int)K, err);
+        return WUSH_OK;
+    }
+    gemm_f16_fused_kernel<<<(int)std::min<int64_t>(tiles, sm_count()), Q_THREADS, Q_TOTAL, st>>>(
+        ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N, (int)K, err);
     return check_launch("gemm_f16_fused");
-}
-
-// The last wave of a persistent tile grid is rarely full (M = 4096, K = 8192: 3584 tiles are 24.2 waves of 148; a
-// shard of 7168 columns 3.03).  Its tiles are cut into K ranges -- a power of two that divides the K steps,
-// leaves ranges of at least 4 steps and makes no more units than there are multiprocessors -- which run side by
-// side; tail_sum_kernel adds them.  {tiles taken whole, ranges per remaining tile}; {tiles, 1} = no cut.
-struct TailPlan { int full_tiles, split; };
-static TailPlan plan_tail(int64_t tiles, int k_steps, bool room)
-{
-    TailPlan p = {(int)tiles, 1};
-    const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0 switches the cut off (measurements, A/B tests)
-    if (!room || (v && v[0] == '0')) return p;
-    const int sms = sm_count();
-    const int full = (int)(tiles / sms) * sms, tail = (int)tiles - full;
-    if (tail == 0) return p;
-    int r = 1;
-    while (tail * r * 2 <= sms && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4) r *= 2;
-    if (r > 1) { p.full_tiles = full; p.split = r; }
-    return p;
 }
 
 template <bool I8>
