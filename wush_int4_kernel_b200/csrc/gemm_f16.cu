@@ -123,6 +123,39 @@ dequant_f16_resident_kernel(const uint8_t* __restrict__ q, const __nv_bfloat16* 
 constexpr int FM = 128, FN = 256;                               // tile; a stage holds 128 bytes of K per row
 constexpr int F_ACC = 2;                                        // TMEM accumulators in rotation (128-row tiles)
 
+// How the tiles of a persistent tile kernel's launch become units of work.  Tiles [0, full_tiles) run over the
+// whole K and write y.  The others leave raw fp32 accumulators of K ranges in 256 x 256 slots of a scratch area and
+// tail_sum_kernel adds a tile's ranges in a fixed order:
+//   mode 1  every other tile in `split` equal ranges (slot = unit index behind the whole tiles);
+//   mode 2  the other tiles' stages, laid end to end, are dealt to the `ctas` CTAs of the grid as contiguous runs
+//           whose bounds are multiples of `gran` stages.  A run is at most one tile long, so it covers the end of one
+//           tile (first piece, slot = CTA index) and possibly the start of the next (second piece, slot = ctas +
+//           that tile's index among the cut tiles); either piece may be empty.  full_tiles is a multiple of ctas and
+//           the grid has exactly `ctas` CTAs, so that CTA c meets the units of run c.
+struct UnitPlan { int n_tiles, k_steps, full_tiles, mode, split, ctas, gran; };
+struct Unit { int tile, ks0, len, slot; };                        // slot < 0: a whole tile
+
+__device__ __forceinline__ int unit_count(const UnitPlan& p) {
+    return p.full_tiles + (p.mode == 1 ? (p.n_tiles - p.full_tiles) * p.split : p.mode == 2 ? 2 * p.ctas : 0);
+}
+__device__ __forceinline__ int run_bound(const UnitPlan& p, int c) {           // first stage of CTA c's run (c = ctas: the end)
+    const long long wg = (long long)(p.n_tiles - p.full_tiles) * p.k_steps / p.gran;
+    return (int)(wg * c / p.ctas) * p.gran;
+}
+__device__ __forceinline__ Unit decode_unit(const UnitPlan& p, int u) {
+    if (u < p.full_tiles) return {u, 0, p.k_steps, -1};
+    const int v = u - p.full_tiles;
+    if (p.mode == 1) {
+        const int rs = p.k_steps / p.split;
+        return {p.full_tiles + v / p.split, (v % p.split) * rs, rs, v};
+    }
+    const int j = v / p.ctas, c = v - j * p.ctas;
+    const int lo = run_bound(p, c), hi = run_bound(p, c + 1);
+    const int tt = lo / p.k_steps, first_end = min(hi, (tt + 1) * p.k_steps);
+    if (j == 0) return {p.full_tiles + tt, lo - tt * p.k_steps, first_end - lo, c};
+    return {p.full_tiles + tt + 1, 0, hi - first_end, p.ctas + tt + 1};
+}
+
 // K-major operand in the 128-byte-swizzled layout TMA writes: rows of 128 B, 8-row groups 1 KB apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
     uint64_t d = 0;
@@ -421,7 +454,7 @@ constexpr int R_TOTAL = R_BARS + (2 * R_STAGES + 2 * R_BUFS + 2 * F_ACC + 1) * 8
 __global__ void __launch_bounds__(R_THREADS, 1)
 gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
                       const unsigned short* __restrict__ ws, const float* __restrict__ down, const TileScale sc,
-                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err, int full_tiles, int ksplit,
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err, const UnitPlan plan,
                       float* __restrict__ part)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -437,8 +470,7 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_m = (M + 2 * FM - 1) / (2 * FM), tiles_n = (N + FN - 1) / FN;
-    const int n_units = full_tiles + (tiles_m * tiles_n - full_tiles) * ksplit;
-    const int all_steps = K / 64, range_steps = all_steps / ksplit, G = K >> 5;     // stages of a whole tile / of a K range
+    const int n_units = unit_count(plan), G = K >> 5;
 
     if (tid == 0) {
         for (int i = 0; i < R_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 17); }
@@ -463,9 +495,8 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int issued = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-                const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / ksplit;
-                const int ks0 = u < full_tiles ? 0 : ((u - full_tiles) % ksplit) * range_steps;
-                const int k_steps = u < full_tiles ? all_steps : range_steps;
+                const Unit un = decode_unit(plan, u);
+                const int t = un.tile, ks0 = un.ks0, k_steps = un.len;
                 const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
                 for (int ks = ks0; ks < ks0 + k_steps; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
@@ -490,7 +521,8 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t idesc = tc::idesc_f16(FN);
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-                const int k_steps = u < full_tiles ? all_steps : range_steps;
+                const int k_steps = decode_unit(plan, u).len;
+                if (k_steps == 0) continue;                                    // an empty piece of a run
                 if (!tc::mbar_wait(&acc_empty[0], aphase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
@@ -523,9 +555,8 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t slot = 0, phase = 0, buf = 0, bphase = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / ksplit;
-            const int ks0 = u < full_tiles ? 0 : ((u - full_tiles) % ksplit) * range_steps;        // a multiple of 4
-            const int ks1 = ks0 + (u < full_tiles ? all_steps : range_steps);
+            const Unit un = decode_unit(plan, u);
+            const int t = un.tile, ks0 = un.ks0, ks1 = un.ks0 + un.len;          // ks0 is a multiple of 4
             const int n = (t / tiles_m) * FN + d;
             const bool live = n < N;
             const float dn = live ? down[n] : 0.f;
@@ -569,9 +600,11 @@ gemm_f16_fused2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t aphase = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / ksplit;
+            const Unit un = decode_unit(plan, u);
+            if (un.len == 0) continue;
+            const int t = un.tile;
             const int m0 = (t % tiles_m) * 2 * FM, n0 = (t / tiles_m) * FN;
-            float* prow = u < full_tiles ? nullptr : part + ((size_t)(u - full_tiles) * (2 * FM) + row) * FN;
+            float* prow = un.slot < 0 ? nullptr : part + ((size_t)un.slot * (2 * FM) + row) * FN;
             if (!tc::mbar_wait(&acc_full[0], aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -648,7 +681,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
 gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TileScale sc,
                       __half* __restrict__ y, int M, int N, int K, int* __restrict__ err,
                       int tile_n_first, int tile_n_count,                     // the column tiles this launch covers
-                      int full_tiles, int tail_split, float* __restrict__ part) // tiles taken whole; K ranges of the others
+                      const UnitPlan plan, float* __restrict__ part)          // tiles taken whole; K ranges of the others
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -662,11 +695,7 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_m = (M + 2 * FM - 1) / (2 * FM), n_tiles = tiles_m * tile_n_count;
     const int k_steps = K / (I8 ? 128 : 64);                 // a stage row is 128 bytes either way
-    // Units of work: the first `full_tiles` tiles (whole waves of the grid) run over the whole K; each of the
-    // remaining tiles -- the last, partly filled wave -- is cut into `tail_split` K ranges that run side by side,
-    // leave their fp32 accumulators in `part` and are summed by tail_sum_kernel.
-    const int n_units = full_tiles + (n_tiles - full_tiles) * tail_split;
-    const int tail_steps = k_steps / tail_split;
+    const int n_units = unit_count(plan);                    // whole tiles, then K ranges of the last wave's tiles
 
     // A dependent launched behind this grid (the widening of the next column tiles) may start as soon as
     // every CTA is resident: it runs in the threads and registers this kernel leaves free.
@@ -694,9 +723,8 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int issued = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-                const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / tail_split;
-                const int ks_first = u < full_tiles ? 0 : ((u - full_tiles) % tail_split) * tail_steps;
-                const int ks_end = u < full_tiles ? k_steps : ks_first + tail_steps;
+                const Unit un = decode_unit(plan, u);
+                const int t = un.tile, ks_first = un.ks0, ks_end = un.ks0 + un.len;
                 const int m0 = (t % tiles_m) * 2 * FM, n0 = (tile_n_first + t / tiles_m) * FN;
                 for (int ks = ks_first; ks < ks_end; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
@@ -721,7 +749,8 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t idesc = I8 ? tc::idesc_i8(FN) : tc::idesc_f16(FN);
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-                const int unit_steps = u < full_tiles ? k_steps : tail_steps;
+                const int unit_steps = decode_unit(plan, u).len;
+                if (unit_steps == 0) continue;                                 // an empty piece of a run
                 if (!tc::mbar_wait(acc_empty, aphase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after();
                 for (int ks = 0; ks < unit_steps; ++ks) {
@@ -758,10 +787,12 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t aphase = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const int t = u < full_tiles ? u : full_tiles + (u - full_tiles) / tail_split;
+            const Unit un = decode_unit(plan, u);
+            if (un.len == 0) continue;
+            const int t = un.tile;
             const int m0 = (t % tiles_m) * 2 * FM, n0 = (tile_n_first + t / tiles_m) * FN;
-            // a K range of a tail tile: raw fp32 (int32) accumulators, 256 x 256 per unit, row-major
-            float* prow = u < full_tiles ? nullptr : part + ((size_t)(u - full_tiles) * (2 * FM) + row) * FN;
+            // a K range of a cut tile: raw fp32 (int32) accumulators, 256 x 256 per slot, row-major
+            float* prow = un.slot < 0 ? nullptr : part + ((size_t)un.slot * (2 * FM) + row) * FN;
             if (!tc::mbar_wait(acc_full, aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -828,33 +859,50 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 1) tc::tmem_dealloc(tmem, 512);
 }
 
-// Sum of the K ranges of the tail tiles (in order: deterministic), scaled and rounded to fp16 once.  One thread per
-// 8 consecutive outputs of a row of a 256 x 256 tile; `part` as written by the tile kernel.
+// Sum of the K ranges of the cut tiles (in a fixed order: deterministic), scaled and rounded to fp16 once.  One
+// thread per 8 consecutive outputs of a row of a 256 x 256 tile; slots as written by the tile kernels.
 template <bool I8>
 __global__ void __launch_bounds__(256)
 tail_sum_kernel(const float* __restrict__ part, const TileScale sc, __half* __restrict__ y, int M, int N, int tiles_m,
-                int tile_n_first, int full_tiles, int tail_split)
+                int tile_n_first, const UnitPlan plan)
 {
-    const int tt = blockIdx.y;                                          // tail tile
+    const int tt = blockIdx.y;                                          // cut tile
     const int e = blockIdx.x * 256 + threadIdx.x;                       // 8-output vector inside the tile
     const int row = e >> 5, col = (e & 31) * 8;
-    const int t = full_tiles + tt;
+    const int t = plan.full_tiles + tt;
     const int m = (t % tiles_m) * 2 * FM + row, n = (tile_n_first + t / tiles_m) * FN + col;
     if (m >= M || n + 8 > N) return;
-    const float* p = part + ((size_t)tt * tail_split * (2 * FM) + row) * FN + col;
+    const float* p = part + (size_t)row * FN + col;                     // + slot * 256 * 256
+    constexpr size_t SLOT = (size_t)(2 * FM) * FN;
     float acc[8];
     int iacc[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) { acc[q] = 0.f; iacc[q] = 0; }
-    for (int r = 0; r < tail_split; ++r) {
-        const float4 a = *reinterpret_cast<const float4*>(p + (size_t)r * (2 * FM) * FN);
-        const float4 b = *reinterpret_cast<const float4*>(p + (size_t)r * (2 * FM) * FN + 4);
+    auto add = [&](int slot) {
+        const float4 a = *reinterpret_cast<const float4*>(p + slot * SLOT);
+        const float4 b = *reinterpret_cast<const float4*>(p + slot * SLOT + 4);
         const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             if constexpr (I8) iacc[q] += __float_as_int(f[q]);
             else acc[q] += f[q];
         }
+    };
+    if (plan.mode == 1) {
+        for (int r = 0; r < plan.split; ++r) add(tt * plan.split + r);
+    } else {
+        // the run that contains the tile's first stage, then every run that starts inside the tile
+        const int tb = tt * plan.k_steps, te = tb + plan.k_steps;
+        const long long wg = (long long)(plan.n_tiles - plan.full_tiles) * plan.k_steps / plan.gran;
+        int c = (int)((long long)(tb / plan.gran) * plan.ctas / wg);
+        while (c > 0 && run_bound(plan, c) > tb) --c;
+        while (c + 1 < plan.ctas && run_bound(plan, c + 1) <= tb) ++c;      // now bound(c) <= tb < bound(c + 1), or c is the last run
+        if (run_bound(plan, c) < tb) {
+            if (run_bound(plan, c + 1) > tb) add(plan.ctas + tt);           // second piece of run c: the start of this tile
+            ++c;
+        }
+        for (; c < plan.ctas && run_bound(plan, c) < te; ++c)
+            if (run_bound(plan, c + 1) > run_bound(plan, c)) add(c);        // first piece of run c
     }
     float fs[8];
     float fm;
@@ -958,9 +1006,9 @@ static bool f16_takes_fused(int64_t M, int64_t N, int64_t K, const void* ws) { r
 // (for a 16-byte-aligned `ws`, which is what wush_w4a4_gemm_workspace_bytes assumes).
 size_t f16_workspace_bytes_min(int64_t M, int64_t N, int64_t K) { return f16_layout_bytes(M, N, K, use_fused(M, N, K)); }
 
-// Room for the fp32 accumulators of the K ranges into which the pre-widened route cuts the tiles of its last,
-// partly filled wave (at most one 256 x 256 tile per multiprocessor).
-static size_t tail_part_bytes() { return (size_t)sm_count() * (2 * FM) * FN * 4; }
+// Room for the fp32 accumulators of the K ranges into which the tile kernels cut the tiles of their last, partly
+// filled wave: at most one 256 x 256 piece per multiprocessor plus one per cut tile.
+static size_t tail_part_bytes() { return (size_t)2 * sm_count() * (2 * FM) * FN * 4; }
 
 size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
@@ -971,21 +1019,31 @@ size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 }
 
 // The last wave of a persistent tile grid is rarely full (M = 4096, K = 8192: 3584 tiles are 24.2 waves of 148; a
-// shard of 7168 columns 3.03).  Its tiles are cut into K ranges -- a power of two that divides the K steps,
-// leaves ranges of at least 4 steps and makes no more units than there are multiprocessors -- which run side by
-// side; tail_sum_kernel adds them.  {tiles taken whole, ranges per remaining tile}; {tiles, 1} = no cut.
-struct TailPlan { int full_tiles, split; };
-static TailPlan plan_tail(int64_t tiles, int k_steps, bool room, int step_multiple = 1)
+// shard of 7168 columns 3.03; M = 256 at N = 57344 1.51).  The tiles beyond the whole waves are cut along K, either
+// into a power-of-two number of equal ranges that all fit one round (mode 1), or -- when they are too many for
+// that -- by dealing their stages to all CTAs as contiguous runs (mode 2); tail_sum_kernel adds the pieces.
+// The choice is by estimate: rounds of stages at `step_us` each, plus what the fp32 pieces cost (measured:
+// about 0.13 us per 256 x 256 piece written and read back, 5 us for the summing kernel), against one whole round.
+static UnitPlan plan_units(int64_t tiles, int k_steps, bool room, int gran, double step_us)
 {
-    TailPlan p = {(int)tiles, 1};
-    const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0 switches the cut off (measurements, A/B tests)
+    UnitPlan p = {(int)tiles, k_steps, (int)tiles, 0, 1, sm_count(), gran};
+    const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0: never cut; 1 / 2: only that mode (measurements, tests)
     if (!room || (v && v[0] == '0')) return p;
     const int sms = sm_count();
     const int full = (int)(tiles / sms) * sms, tail = (int)tiles - full;
     if (tail == 0) return p;
+    double best = k_steps * step_us;                                   // the last wave as it is
     int r = 1;
-    while (tail * r * 2 <= sms && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4 && (k_steps / (r * 2)) % step_multiple == 0) r *= 2;
-    if (r > 1) { p.full_tiles = full; p.split = r; }
+    while (tail * r * 2 <= sms && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4 && (k_steps / (r * 2)) % gran == 0) r *= 2;
+    if (r > 1 && !(v && v[0] == '2')) {
+        const double est = (k_steps / r) * step_us + tail * r * 0.13 + 5.0;
+        if (est < best || (v && v[0] == '1')) { best = est; p.full_tiles = full; p.mode = 1; p.split = r; }
+    }
+    if (k_steps % gran == 0 && !(v && v[0] == '1')) {
+        const long long wg = (long long)tail * k_steps / gran;
+        const double est = (double)((wg + sms - 1) / sms) * gran * step_us + (sms + tail) * 0.13 + 5.0;
+        if (wg >= sms && (est < best || (v && v[0] == '2'))) { best = est; p.full_tiles = full; p.mode = 2; p.split = 1; }
+    }
     return p;
 }
 
@@ -1021,16 +1079,16 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
     const TileScale sc = {fa, fb, 0.f, nullptr};
     if (wide) {
         // few tiles: every tile in `split` K ranges; many tiles: only those of the last, partly filled wave
-        TailPlan tp = {0, split};
-        if (split == 1) tp = plan_tail(tiles, (int)(K / 64), part_room && aligned16(y), 4);
-        const int64_t units = tp.full_tiles + (tiles - tp.full_tiles) * tp.split;
+        UnitPlan up = {(int)tiles, (int)(K / 64), 0, 1, split, sm_count(), 4};
+        if (split == 1) up = plan_units(tiles, (int)(K / 64), part_room && aligned16(y), 4, 1.07);
+        const int64_t units = up.mode == 2 ? sm_count()
+                                           : up.full_tiles + (up.mode == 1 ? (tiles - up.full_tiles) * up.split : 0);
         gemm_f16_fused2_kernel<<<(int)std::min<int64_t>(units, sm_count()), R_THREADS, R_TOTAL, st>>>(
-            ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N, (int)K, err, tp.full_tiles, tp.split, part);
+            ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N, (int)K, err, up, part);
         if (int s2 = check_launch("gemm_f16_fused")) return s2;
-        if (tp.split > 1) {
-            const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - tp.full_tiles));
-            tail_sum_kernel<false><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, (int)((M + 2 * FM - 1) / (2 * FM)), 0,
-                                                        tp.full_tiles, tp.split);
+        if (up.mode != 0) {
+            const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - up.full_tiles));
+            tail_sum_kernel<false><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, (int)((M + 2 * FM - 1) / (2 * FM)), 0, up);
             return check_launch("tail_sum");
         }
         return WUSH_OK;
@@ -1046,14 +1104,14 @@ static int launch_tile2(const CUtensorMap& ma, const CUtensorMap& mb, const Tile
 {
     const int tiles_m = (int)((M + 2 * FM - 1) / (2 * FM));
     const int64_t tiles = (int64_t)tiles_m * tile_n_count;
-    const TailPlan tp = plan_tail(tiles, (int)(K / (I8 ? 128 : 64)), part != nullptr);
-    const int64_t units = tp.full_tiles + (tiles - tp.full_tiles) * tp.split;
+    const UnitPlan up = plan_units(tiles, (int)(K / (I8 ? 128 : 64)), part != nullptr, 1, I8 ? 0.4 : 0.8);
+    const int64_t units = up.mode == 2 ? sm_count() : up.full_tiles + (up.mode == 1 ? (tiles - up.full_tiles) * up.split : 0);
     gemm_tile2_kernel<I8><<<(int)std::min<int64_t>(units, sm_count()), T_THREADS, T_TOTAL, st>>>(
-        ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, tile_n_first, tile_n_count, tp.full_tiles, tp.split, part);
+        ma, mb, sc, (__half*)y, (int)M, (int)N, (int)K, err, tile_n_first, tile_n_count, up, part);
     if (int s = check_launch("gemm_tile2")) return s;
-    if (tp.split > 1) {
-        const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - tp.full_tiles));
-        tail_sum_kernel<I8><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, tiles_m, tile_n_first, tp.full_tiles, tp.split);
+    if (up.mode != 0) {
+        const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - up.full_tiles));
+        tail_sum_kernel<I8><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, tiles_m, tile_n_first, up);
         return check_launch("tail_sum");
     }
     return WUSH_OK;
