@@ -274,6 +274,369 @@ def test_last_wave_in_k_ranges(dev, orc, shape, mode, monkeypatch):
     assert float((d > 0).float().mean()) < 0.2
 
 
+def test_decode_tcgen05_exact_group_sums(dev, orc):
+    """One group per row with unit scales: the fp16 result IS the integer group sum (|P| <= 2048 is exact
+    in fp16), so the tensor-core path's per-group sums are checked exactly -- including code -8."""
+    M, N, K = 32, 256, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    xq = torch.randint(0, 256, (M, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    # only group 0 carries a non-zero scale: Y = P_0
+    xs = torch.zeros(M, K // 32, dtype=torch.bfloat16, device=dev)
+    ws = torch.zeros(N, K // 32, dtype=torch.bfloat16, device=dev)
+    for grp in range(K // 32):
+        xs.zero_(); ws.zero_()
+        xs[:, grp] = 1.0
+        ws[:, grp] = 1.0
+        y = cabi.gemm(xq, xs, wq, ws, variant=capi.GEMM_DECODE_TC)
+        P = orc.group_partials(xq.cpu().numpy(), wq.cpu().numpy())[:, :, grp]
+        assert np.array_equal(y.float().cpu().numpy(), P.astype(np.float32)), grp
+
+
+def test_decode_tcgen05_needs_scratch(dev):
+    """The explicit variant refuses to run without its scratch; AUTO (the streaming kernel here) needs none."""
+    lib = capi.load()
+    M, N, K = 8, 512, 1024
+    z = torch.zeros(N * K // 2, dtype=torch.uint8, device=dev)
+    s = torch.zeros(N * K // 32, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, N, dtype=torch.float16, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.wush_w4a4_gemm_workspace_bytes(M, N, K, capi.GEMM_DECODE_TC) > 256
+    assert lib.wush_w4a4_gemm(z.data_ptr(), s.data_ptr(), z.data_ptr(), s.data_ptr(), M, N, K, y.data_ptr(),
+                              capi.GEMM_DECODE_TC, None, 0, st) == capi.WUSH_ERR_WORKSPACE
+    assert lib.wush_w4a4_gemm(z.data_ptr(), s.data_ptr(), z.data_ptr(), s.data_ptr(), M, N, K, y.data_ptr(),
+                              capi.GEMM_AUTO, None, 0, st) == capi.WUSH_OK
+    torch.cuda.synchronize()
+    assert (y == 0).all()
+
+
+def test_auto_variant_by_shape(dev):
+    """What AUTO stands for: the GEMV for one or two rows, the streaming kernel for decode batches and for
+    mid-size M on narrow layers, the fp16 route where its tiles (or K ranges) fill the machine."""
+    lib = capi.load()
+    pick = lib.wush_w4a4_gemm_pick_variant
+    assert pick(1, 57344, 8192) == capi.GEMM_GEMV and pick(2, 8192, 8192) == capi.GEMM_GEMV
+    assert pick(4, 57344, 8192) == capi.GEMM_DECODE and pick(4, 8192, 8192) == capi.GEMM_GEMV
+    assert pick(16, 57344, 8192) == capi.GEMM_DECODE and pick(32, 24576, 4096) == capi.GEMM_DECODE
+    assert pick(64, 8192, 8192) == capi.GEMM_DECODE and pick(128, 8192, 3584) == capi.GEMM_DECODE
+    assert pick(128, 57344, 8192) == capi.GEMM_TILE_F16 and pick(256, 8192, 8192) == capi.GEMM_TILE_F16
+    assert pick(4096, 57344, 8192) == capi.GEMM_TILE_F16
+    assert pick(48, 64, 96) == capi.GEMM_DECODE                   # K no tile kernel takes: the generic decode path
+    for shape in [(1, 64, 64), (300, 1000, 4096), (96, 24576, 4096)]:
+        v = pick(*shape)
+        assert lib.wush_w4a4_gemm_workspace_bytes(*shape, capi.GEMM_AUTO) == lib.wush_w4a4_gemm_workspace_bytes(*shape, v)
+
+
+def test_f16_route_wide_scale_range(dev, orc):
+    """Rows whose group scales span many octaves (and exact-zero groups) through the fp16-folded route."""
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 160, 264, 512
+    X = (torch.randn(M, K, generator=g) * torch.exp2(torch.randint(-12, 8, (M, K // 32), generator=g).float()).repeat_interleave(32, 1))
+    W = (torch.randn(N, K, generator=g) * torch.exp2(torch.randint(-14, 2, (N, K // 32), generator=g).float()).repeat_interleave(32, 1))
+    X[3] = 0
+    W[:, 64:96] = 0
+    xq, xs = orc.quant_int4(orc.bits(X.to(torch.bfloat16)))
+    wq, ws = orc.quant_int4(orc.bits(W.to(torch.bfloat16)))
+    y64 = orc.gemm_f64(xq, xs, wq, ws)
+    y = cabi.gemm(*_to_dev(dev, xq, xs, wq, ws), variant=capi.GEMM_TILE_F16)
+    assert torch.isfinite(y.float()).all()
+    _assert_close(y, y64, "wide")
+    assert (y[3] == 0).all()
+
+
+SHAPES = [(64, 96, 128), (1, 64, 64), (300, 500, 512), (130, 512, 4096), (8, 4096, 4096),   # reference tests/test_p13.py:18
+          (257, 33, 96), (8, 8, 32), (4, 100, 256), (2, 77, 512), (3, 64, 96), (17, 130, 768), (32, 256, 1024),
+          (5, 129, 256), (33, 64, 256)]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_gemm_auto_vs_fp64(dev, orc, shape):
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=M * 7 + N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    y = cabi.gemm(*_to_dev(dev, *ops))
+    _assert_close(y, y64, shape)
+
+
+def test_gemm_every_variant(dev, orc):
+    for (M, N, K) in [(1, 200, 512), (4, 130, 256), (3, 64, 96)]:
+        ops = _operands(M, N, K, seed=11, orc=orc)
+        y64 = orc.gemm_f64(*ops)
+        d = _to_dev(dev, *ops)
+        for v in (capi.GEMM_GEMV, capi.GEMM_DECODE, capi.GEMM_TILE, capi.GEMM_AUTO):
+            _assert_close(cabi.gemm(*d, variant=v), y64, (M, N, K, v))
+    for (M, N, K) in [(16, 300, 512), (32, 128, 256), (100, 260, 768)]:
+        ops = _operands(M, N, K, seed=12, orc=orc)
+        y64 = orc.gemm_f64(*ops)
+        d = _to_dev(dev, *ops)
+        for v in (capi.GEMM_DECODE, capi.GEMM_TILE, capi.GEMM_AUTO):
+            _assert_close(cabi.gemm(*d, variant=v), y64, (M, N, K, v))
+    with pytest.raises(capi.WushError):
+        cabi.gemm(*_to_dev(dev, *_operands(8, 16, 64, 1, orc)), variant=capi.GEMM_GEMV)
+
+
+def test_gemm_golden(dev, orc, golden):
+    z = golden("w4a4_matmul")
+    for (M, N, K) in z["shapes"]:
+        k = f"{M}x{N}x{K}"
+        d = _to_dev(dev, z[k + "_xq"], z[k + "_xs"], z[k + "_wq"], z[k + "_ws"])
+        _assert_close(cabi.gemm(*d), z[k + "_y64"], k)
+
+
+def test_zero_activations_give_exact_zero(dev, orc):
+    # reference tests/test_s3.py:43-48
+    g = torch.Generator().manual_seed(0)
+    for M, N, K in [(4, 16, 64), (1, 64, 256), (16, 128, 256), (40, 130, 512)]:
+        xq, xs = orc.quant_int4(np.zeros((M, K), np.uint16))
+        wq, ws = orc.quant_int4(orc.bits(torch.randn(N, K, generator=g).to(torch.bfloat16)))
+        y = cabi.gemm(*_to_dev(dev, xq, xs, wq, ws))
+        assert (y == 0).all()
+
+
+def test_code_minus_eight_is_sign_extended(dev, orc):
+    # the sigma path never emits -8, but consumers must handle it (reference tests/test_s4c.py:13)
+    rng = np.random.default_rng(0)
+    for M, N, K in [(1, 64, 128), (8, 64, 256), (40, 64, 256)]:
+        xq = rng.integers(0, 256, (M, K // 2), dtype=np.uint8)
+        wq = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+        ones = np.full((M, K // 32), 0x3F80, np.uint16)
+        onesw = np.full((N, K // 32), 0x3F80, np.uint16)
+        y64 = orc.gemm_f64(xq, ones, wq, onesw)
+        _assert_close(cabi.gemm(*_to_dev(dev, xq, ones, wq, onesw)), y64, (M, N, K))
+        P = cabi.group_partials(torch.from_numpy(xq).to(dev), torch.from_numpy(wq).to(dev))
+        assert np.array_equal(P.cpu().numpy(), orc.group_partials(xq, wq))
+
+
+def test_group_partials_exact(dev, orc):
+    # the last three shapes run on the tcgen05 tile path (M > 32, K % 256 == 0, N % 8 == 0)
+    for (M, N, K) in [(8, 16, 64), (33, 130, 256), (5, 64, 1024), (64, 96, 128), (130, 136, 512), (128, 256, 256),
+                      (200, 72, 768)]:
+        xq, _, wq, _ = _operands(M, N, K, seed=5, orc=orc)
+        P = cabi.group_partials(torch.from_numpy(xq).to(dev), torch.from_numpy(wq).to(dev))
+        assert np.array_equal(P.cpu().numpy(), orc.group_partials(xq, wq)), (M, N, K)
+
+
+def test_atom_selftest(dev):
+    rng = np.random.default_rng(1)
+    a = rng.integers(-8, 8, (8, 32), dtype=np.int8)
+    b = rng.integers(-8, 8, (32, 8), dtype=np.int8)
+    c = cabi.atom(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev))
+    assert np.array_equal(c.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32))
+    from my_int4 import _C
+    c2 = _C.s4_atom_selftest(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev))
+    assert np.array_equal(c2.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32))
+
+
+def test_operator_shapes_and_errors(dev, orc):
+    from my_int4 import _C
+    ops = _operands(6, 40, 128, seed=3, orc=orc)
+    xq, xs, wq, ws = _to_dev(dev, *ops)
+    y64 = orc.gemm_f64(*ops)
+    y = _C.w4a4_gemm(xq.reshape(2, 3, -1), xs.reshape(2, 3, -1), wq, ws)
+    assert y.shape == (2, 3, 40) and y.dtype == torch.float16        # v0 keeps leading dims
+    _assert_close(y, y64, "v0")
+    for fn in (_C.w4a4_gemm_v1, _C.w4a4_gemm_v2, _C.w4a4_gemm_s4, _C.w4a4_gemv_multi):
+        y = fn(xq.reshape(2, 3, -1), xs.reshape(2, 3, -1), wq, ws)
+        assert y.shape == (6, 40)
+        _assert_close(y, y64, fn.__name__)
+    y1 = _C.w4a4_gemv(xq[:1], xs[:1], wq, ws)
+    assert y1.shape == (40,)
+    _assert_close(y1, y64[:1], "gemv")
+    with pytest.raises(RuntimeError):
+        _C.w4a4_gemv(xq, xs, wq, ws)                                   # more than one row
+    with pytest.raises(RuntimeError):
+        _C.w4a4_gemm_s4(xq, xs, wq[:, :32].contiguous(), ws)           # K mismatch
+    with pytest.raises(RuntimeError):
+        _C.w4a4_gemm_s4(xq, xs.float(), wq, ws)                        # wrong scale dtype
+    big = _operands(33, 16, 64, seed=4, orc=orc)
+    with pytest.raises(RuntimeError):
+        _C.w4a4_gemv_multi(*_to_dev(dev, *big))                        # more than 32 rows
+
+
+# ------------------------------------------------------------------------------------------
+# per-tensor route
+# ------------------------------------------------------------------------------------------
+def test_per_tensor_route(dev, orc, golden):
+    from my_int4 import _C
+    z = golden("per_tensor")
+    for name in ("randn", "sweep"):
+        x = _bf16(z[name + "_x"], dev)
+        scale = float(z[name + "_scale"])
+        q = _C.quant_int4_tensor_scale(x, scale)
+        assert q.dim() == 1 and np.array_equal(q.cpu().numpy(), z[name + "_q"]), name
+        inv = torch.tensor([1.0 / scale], dtype=torch.float32, device=dev)
+        q2 = _C.quant_int4_tensor_scale_dev(x, inv)
+        assert torch.equal(q, q2)
+    rng = np.random.default_rng(2)
+    for (M, N, K) in [(64, 96, 128), (1, 64, 256), (30, 50, 512)]:
+        xq = rng.integers(0, 256, (M, K // 2), dtype=np.uint8)
+        wq = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+        alpha = 0.0123
+        yo, _ = orc.gemm_tensor_scale(xq, wq, alpha)
+        y = _C.w4a4_gemm_cutlass(torch.from_numpy(xq).to(dev), torch.from_numpy(wq).to(dev), alpha)
+        assert y.shape == (M, N) and np.array_equal(orc.bits(y), yo), (M, N, K)
+        a = torch.tensor([alpha], dtype=torch.float32, device=dev)
+        y2 = _C.w4a4_gemm_cutlass_dev(torch.from_numpy(xq).reshape(-1).to(dev), torch.from_numpy(wq).to(dev), a)
+        assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 264, 384), (512, 1000, 1024), (4096, 4096, 4096)])
+def test_per_tensor_tile_route(dev, orc, M, N, K):
+    """tcgen05 kind::i8 tiles for the per-tensor product: same bits as the scratch-free kernel
+    (and as the oracle where the oracle finishes quickly), error word clean."""
+    from tests import cabi
+    gen = torch.Generator(device=dev).manual_seed(M + N + K)
+    xq = torch.randint(0, 256, (M, K // 2), generator=gen, device=dev, dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=gen, device=dev, dtype=torch.uint8)
+    alpha = 3.1e-4
+    y, nbytes, flag = cabi.gemm_ts_ws(xq, wq, alpha)
+    assert nbytes > 0 and flag == 0
+    assert torch.equal(y, cabi.gemm_ts(xq, wq, alpha))
+    a = torch.tensor([alpha], dtype=torch.float32, device=dev)
+    y2, _, flag2 = cabi.gemm_ts_ws(xq, wq, 0.0, a)
+    assert flag2 == 0 and torch.equal(y, y2)
+    if M * N * K <= 1 << 28:
+        yo, _ = orc.gemm_tensor_scale(xq.cpu().numpy(), wq.cpu().numpy(), alpha)
+        assert np.array_equal(orc.bits(y), yo)
+    # the binding allocates the scratch itself
+    from my_int4 import _C
+    assert torch.equal(_C.w4a4_gemm_cutlass(xq, wq, alpha), y)
+
+
+# ------------------------------------------------------------------------------------------
+# CUDA Graph safety (reference tests/test_p13.py:45-66, tests/test_p12.py:142-152)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M", [1, 8, 48])
+def test_graph_replay_equals_eager(dev, M):
+    from my_int4 import _C
+    from wush_int4_kernel_b200 import synth
+    from wush_int4_kernel_b200.linear import W4A4Linear
+
+    _C.init()
+    layer = synth.make_layer(512, 384, seed=2, device="cuda", quantiser=_C.quant_int4)
+    lin = W4A4Linear(layer.t_bf16, layer.wq, layer.ws)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = synth.draw_activations(M, 512, layer.outliers, gen)
+    y0 = lin(x).clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            lin(x)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = lin(x)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, y0)                     # deterministic kernels: bit identical
+    x.copy_(synth.draw_activations(M, 512, layer.outliers, gen))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, lin(x))
+
+
+# ------------------------------------------------------------------------------------------
+# the reference's end-to-end accuracy gate on outlier data (tests/test_p13.py:29-43)
+# ------------------------------------------------------------------------------------------
+def test_end_to_end_outlier_gate(dev):
+    from my_int4 import _C
+    from my_int4.wush_transform import compute_wush_transform, transform_weights
+
+    torch.manual_seed(0)
+    M, N, K, G = 2048, 512, 4096, 32
+    X = torch.randn(M, K, dtype=torch.bfloat16, device=dev)
+    X[:, 5::G] *= 15.0
+    W = torch.randn(N, K, dtype=torch.bfloat16, device=dev)
+    W[:, 12::G] *= 8.0
+    Yt = X.double() @ W.double().t()
+    Xc = torch.randn(256, K, device=dev)
+    Xc[:, 5::G] *= 15.0
+    T64 = compute_wush_transform(Xc, W.float(), group_size=G)
+    Ww = transform_weights(W.double(), T64).to(torch.bfloat16).contiguous()
+    wq, ws = _C.quant_int4(Ww)
+    xq, xs = _C.fused_transform_quant_int4_v3(X, T64.to(torch.bfloat16))
+    err = ((_C.w4a4_gemm_s4(xq, xs, wq, ws).double() - Yt).norm() / Yt.norm()).item()
+    assert err <= 0.082, err
+    xq0, xs0 = _C.quant_int4(X)
+    wq0, ws0 = _C.quant_int4(W)
+    bare = ((_C.w4a4_gemm_s4(xq0, xs0, wq0, ws0).double() - Yt).norm() / Yt.norm()).item()
+    assert bare > 0.3                                # the transform is what brings 53 % down to 7.8 %
+
+
+# ------------------------------------------------------------------------------------------
+# full benchmark sizes: size-independent properties instead of a full CPU product
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("K,N", [(4096, 24576), (8192, 57344)])
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_full_size_decode_sampled_columns(dev, orc, K, N, M):
+    """Random weights at the benchmark shapes; a seeded sample of output columns must agree
+    with the oracle, a zeroed activation row must give an exactly zero output row, and a
+    permutation of the weight rows must permute the output columns bit for bit."""
+    g = torch.Generator(device="cuda").manual_seed(K + M)
+    wq = torch.randint(0, 256, (N, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    ws = (0.01 * (1 + 0.2 * torch.rand(N, K // 32, generator=g, device=dev))).to(torch.bfloat16)
+    xq = torch.randint(0, 256, (M, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    xs = (0.5 * (1 + torch.rand(M, K // 32, generator=g, device=dev))).to(torch.bfloat16)
+    if M > 1:
+        xq[M - 1].zero_()
+    y = cabi.gemm(xq, xs, wq, ws)
+    cols = torch.randperm(N, generator=g, device=dev)[:256].sort().values
+    y64 = orc.gemm_f64(xq.cpu().numpy(), orc.bits(xs), wq[cols].cpu().numpy(), orc.bits(ws[cols]))
+    _assert_close(y[:, cols], y64, (M, N, K))
+    if M > 1:
+        assert (y[M - 1] == 0).all()
+    perm = torch.randperm(N, generator=g, device=dev)
+    y_perm = cabi.gemm(xq, xs, wq[perm].contiguous(), ws[perm].contiguous())
+    assert torch.equal(y_perm, y[:, perm])
+
+
+def test_full_size_prefill_sampled(dev, orc):
+    K, N, M = 8192, 57344, 512
+    g = torch.Generator(device="cuda").manual_seed(9)
+    wq = torch.randint(0, 256, (N, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    ws = (0.01 * (1 + 0.2 * torch.rand(N, K // 32, generator=g, device=dev))).to(torch.bfloat16)
+    xq = torch.randint(0, 256, (M, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    xs = (0.5 * (1 + torch.rand(M, K // 32, generator=g, device=dev))).to(torch.bfloat16)
+    y = cabi.gemm(xq, xs, wq, ws)
+    cols = torch.randperm(N, generator=g, device=dev)[:64].sort().values
+    rows = torch.randperm(M, generator=g, device=dev)[:64].sort().values
+    y64 = orc.gemm_f64(xq[rows].cpu().numpy(), orc.bits(xs[rows]), wq[cols].cpu().numpy(), orc.bits(ws[cols]))
+    _assert_close(y[rows][:, cols], y64, "prefill")
+
+
+def test_full_size_fused_tq_roundtrip(dev, orc):
+    """M=4096, K=8192 activations: FAST vs EXACT flip rate at full size, and EXACT vs the
+    oracle on a sample of rows."""
+    from wush_int4_kernel_b200 import synth
+    from my_int4 import _C
+    layer = synth.make_layer(8192, 256, seed=4, device="cuda", quantiser=_C.quant_int4)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = synth.draw_activations(4096, 8192, layer.outliers, gen)
+    qe, se = cabi.fused_tq(x, layer.t_bf16, capi.TQ_EXACT)
+    qf, sf = cabi.fused_tq(x, layer.t_bf16, capi.TQ_FAST)
+    ne, nf = _nibbles(qe.cpu().numpy()).astype(np.int32), _nibbles(qf.cpu().numpy()).astype(np.int32)
+    d = ne - nf
+    assert np.abs(d).max() <= 1 and (d != 0).mean() <= 1e-4
+    rows = torch.arange(0, 4096, 257, device=dev)
+    qo, so = orc.fused_tq(orc.bits(x[rows]), orc.bits(layer.t_bf16))
+    assert np.array_equal(qe[rows].cpu().numpy(), qo) and np.array_equal(orc.bits(se[rows]), so)
+
+
+# ------------------------------------------------------------------------------------------
+# tcgen05 plumbing: one kind::i8 instruction tile (descriptor / TMEM / tcgen05.ld mapping)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [16, 64, 128, 256])
+def test_tcgen05_i8_tile(dev, n):
+    rng = np.random.default_rng(n)
+    a = rng.integers(-128, 128, (128, 32), dtype=np.int8)
+    b = rng.integers(-128, 128, (n, 32), dtype=np.int8)
+    d, status = cabi.tile_selftest(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev))
+    assert status == 0, "bounded wait on the MMA barrier gave up"
+    assert np.array_equal(d.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32).T)
+
+
 @pytest.mark.parametrize("M,N,K", [(2100, 264, 512), (2100, 512, 512), (256, 520, 512), (130, 264, 320), (300, 512, 1024)])
 def test_output_and_scratch_on_16_byte_boundaries(M, N, K):
     """The tile kernels and their pre-passes store 32 bytes per lane where the addresses allow it.  A caller may
