@@ -252,7 +252,8 @@ def test_pair_tile_kernel_equals_single_cta_kernel(dev, orc, shape, monkeypatch)
 
 @pytest.mark.parametrize("mode", ["1", "2"])
 @pytest.mark.parametrize("shape", [(2100, 264, 512), (2304, 2048, 1024), (4096, 1536, 2048), (2100, 9472, 256),
-                                   (260, 4096, 2048), (520, 2048, 4096), (300, 520, 1024)])
+                                   (260, 4096, 2048), (520, 2048, 4096), (300, 520, 1024),
+                                   (100, 19456, 512), (100, 38400, 512)])      # the 128-row kernel: 76 and 150 tiles
 def test_last_wave_in_k_ranges(dev, orc, shape, mode, monkeypatch):
     """The tiles of the last, partly filled wave are cut along K and summed afterwards: mode 1 = equal ranges that
     fit one round, mode 2 = their stages dealt to all CTAs as contiguous runs (a run may end one tile and begin the

@@ -247,7 +247,8 @@ row_shift_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ up, fl
 __global__ void __launch_bounds__(Q_THREADS, 1)
 gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
                       const unsigned short* __restrict__ ws, const float* __restrict__ down, const TileScale sc,
-                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err)
+                      __half* __restrict__ y, int M, int N, int K, int* __restrict__ err, const UnitPlan plan,
+                      float* __restrict__ part)                      // units of work as in the 256-row kernel below; slots of 128 x 256
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -261,8 +262,8 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tiles_m = (M + FM - 1) / FM, tiles_n = (N + FN - 1) / FN, n_tiles = tiles_m * tiles_n;
-    const int k_steps = K / 64, G = K >> 5;
+    const int tiles_m = (M + FM - 1) / FM, n_units = unit_count(plan);
+    const int G = K >> 5;
 
     if (tid == 0) {
         for (int i = 0; i < Q_STAGES; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 17); }
@@ -286,9 +287,11 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             uint32_t slot = 0, phase = 0;
             int issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const Unit un = decode_unit(plan, u);
+                const int t = un.tile;
                 const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
-                for (int ks = 0; ks < k_steps; ++ks) {
+                for (int ks = un.ks0; ks < un.ks0 + un.len; ++ks) {
                     if (!tc::mbar_wait(&empty[slot], phase ^ 1)) { ok = false; break; }
                     uint8_t* st = smem + slot * Q_STAGE;
                     tc::mbar_expect_tx(&full[slot], QA_BYTES + QP_BYTES);
@@ -310,7 +313,9 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             uint32_t slot = 0, phase = 0, buf = 0, bphase = 0, ab = 0, aphase = 0;
             const uint32_t idesc = tc::idesc_f16(FN);
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const int k_steps = decode_unit(plan, u).len;
+                if (k_steps == 0) continue;                                    // an empty piece of a run
                 if (!tc::mbar_wait(&acc_empty[ab], aphase ^ 1)) { ok = false; break; }
                 tc::tc_fence_after();
                 for (int ks = 0; ks < k_steps; ++ks) {
@@ -340,18 +345,20 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int d = (tid - 256) & 255, g = (tid - 256) >> 8;     // weight row of the tile, group of the stage
         uint32_t slot = 0, phase = 0, buf = 0, bphase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const Unit un = decode_unit(plan, u);
+            const int t = un.tile, ks0 = un.ks0, ks1 = un.ks0 + un.len;          // ks0 is a multiple of 4
             const int n = (t / tiles_m) * FN + d;
             const bool live = n < N;
             const float dn = live ? down[n] : 0.f;
             // scales: one 16-byte load covers this row's 8 groups = 4 stages; the next one is in flight meanwhile
             const uint4* srow = reinterpret_cast<const uint4*>(ws + (size_t)(live ? n : 0) * G);
             const uint4 zero4 = make_uint4(0, 0, 0, 0);
-            uint4 s_cur = zero4, s_nxt = live ? __ldg(srow) : zero4;
-            for (int ks = 0; ks < k_steps; ++ks) {
+            uint4 s_cur = zero4, s_nxt = live ? __ldg(srow + (ks0 >> 2)) : zero4;
+            for (int ks = ks0; ks < ks1; ++ks) {
                 if ((ks & 3) == 0) {
                     s_cur = s_nxt;
-                    if (live && ks + 4 < k_steps) s_nxt = __ldg(srow + (ks >> 2) + 1);
+                    if (live && ks + 4 < ks1) s_nxt = __ldg(srow + (ks >> 2) + 1);
                 }
                 const uint32_t pair = (ks & 2) ? ((ks & 1) ? s_cur.w : s_cur.z) : ((ks & 1) ? s_cur.y : s_cur.x);   // groups 2ks, 2ks+1
                 const float s_f = g ? bf16_hi(pair) : bf16_lo(pair);
@@ -381,8 +388,12 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         uint32_t ab = 0, aphase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const Unit un = decode_unit(plan, u);
+            if (un.len == 0) continue;
+            const int t = un.tile;
             const int m0 = (t % tiles_m) * FM, n0 = (t / tiles_m) * FN;
+            float* prow = un.slot < 0 ? nullptr : part + ((size_t)un.slot * FM + row) * FN;
             if (!tc::mbar_wait(&acc_full[ab], aphase)) { ok = false; break; }
             tc::tc_fence_after();
             const int m = m0 + row;
@@ -398,7 +409,12 @@ gemm_f16_fused_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (lane == 0) tc::mbar_arrive(&acc_empty[ab]);
                 }
                 const int n = n0 + c * 32;
-                if (m < M && n < N) {
+                if (prow) {                                     // 128 bytes per lane: four 32-byte stores
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        st_global_v8(prow + c * 32 + q * 8, make_uint4(v[q * 8], v[q * 8 + 1], v[q * 8 + 2], v[q * 8 + 3]),
+                                     make_uint4(v[q * 8 + 4], v[q * 8 + 5], v[q * 8 + 6], v[q * 8 + 7]));
+                } else if (m < M && n < N) {
                     __half* yr = y + (size_t)m * N + n;
                     const bool wide = ((reinterpret_cast<uintptr_t>(y) & 31) == 0) && (N & 15) == 0;   // 32-byte stores possible
                     uint4 prev = make_uint4(0, 0, 0, 0);
@@ -861,7 +877,7 @@ gemm_tile2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
 // Sum of the K ranges of the cut tiles (in a fixed order: deterministic), scaled and rounded to fp16 once.  One
 // thread per 8 consecutive outputs of a row of a 256 x 256 tile; slots as written by the tile kernels.
-template <bool I8>
+template <bool I8, int ROWS>
 __global__ void __launch_bounds__(256)
 tail_sum_kernel(const float* __restrict__ part, const TileScale sc, __half* __restrict__ y, int M, int N, int tiles_m,
                 int tile_n_first, const UnitPlan plan)
@@ -870,10 +886,10 @@ tail_sum_kernel(const float* __restrict__ part, const TileScale sc, __half* __re
     const int e = blockIdx.x * 256 + threadIdx.x;                       // 8-output vector inside the tile
     const int row = e >> 5, col = (e & 31) * 8;
     const int t = plan.full_tiles + tt;
-    const int m = (t % tiles_m) * 2 * FM + row, n = (tile_n_first + t / tiles_m) * FN + col;
+    const int m = (t % tiles_m) * ROWS + row, n = (tile_n_first + t / tiles_m) * FN + col;
     if (m >= M || n + 8 > N) return;
-    const float* p = part + (size_t)row * FN + col;                     // + slot * 256 * 256
-    constexpr size_t SLOT = (size_t)(2 * FM) * FN;
+    const float* p = part + (size_t)row * FN + col;                     // + slot * ROWS * 256
+    constexpr size_t SLOT = (size_t)ROWS * FN;
     float acc[8];
     int iacc[8];
 #pragma unroll
@@ -1014,8 +1030,7 @@ size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
     // K ranges exist on the pre-widened route, on the 256-row kernel with in-kernel widening (M > 128) and where few
     // tiles are cut into ranges as a whole; their accumulators live behind the layout, on a 256-byte boundary
-    if (!use_fused(M, N, K) || M > FM || f16_fused_split(M, N, K) > 1) return f16_workspace_bytes_min(M, N, K) + tail_part_bytes() + 256;
-    return f16_workspace_bytes_min(M, N, K);
+    return f16_workspace_bytes_min(M, N, K) + tail_part_bytes() + 256;
 }
 
 // The last wave of a persistent tile grid is rarely full (M = 4096, K = 8192: 3584 tiles are 24.2 waves of 148; a
@@ -1024,7 +1039,7 @@ size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 // that -- by dealing their stages to all CTAs as contiguous runs (mode 2); tail_sum_kernel adds the pieces.
 // The choice is by estimate: rounds of stages at `step_us` each, plus what the fp32 pieces cost (measured:
 // about 0.13 us per 256 x 256 piece written and read back, 5 us for the summing kernel), against one whole round.
-static UnitPlan plan_units(int64_t tiles, int k_steps, bool room, int gran, double step_us)
+static UnitPlan plan_units(int64_t tiles, int k_steps, bool room, int gran, double step_us, double piece_us = 0.13)
 {
     UnitPlan p = {(int)tiles, k_steps, (int)tiles, 0, 1, sm_count(), gran};
     const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0: never cut; 1 / 2: only that mode (measurements, tests)
@@ -1036,12 +1051,12 @@ static UnitPlan plan_units(int64_t tiles, int k_steps, bool room, int gran, doub
     int r = 1;
     while (tail * r * 2 <= sms && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4 && (k_steps / (r * 2)) % gran == 0) r *= 2;
     if (r > 1 && !(v && v[0] == '2')) {
-        const double est = (k_steps / r) * step_us + tail * r * 0.13 + 5.0;
+        const double est = (k_steps / r) * step_us + tail * r * piece_us + 5.0;
         if (est < best || (v && v[0] == '1')) { best = est; p.full_tiles = full; p.mode = 1; p.split = r; }
     }
     if (k_steps % gran == 0 && !(v && v[0] == '1')) {
         const long long wg = (long long)tail * k_steps / gran;
-        const double est = (double)((wg + sms - 1) / sms) * gran * step_us + (sms + tail) * 0.13 + 5.0;
+        const double est = (double)((wg + sms - 1) / sms) * gran * step_us + (sms + tail) * piece_us + 5.0;
         if (wg >= sms && (est < best || (v && v[0] == '2'))) { best = est; p.full_tiles = full; p.mode = 2; p.split = 1; }
     }
     return p;
@@ -1088,14 +1103,22 @@ static int f16_fused_dispatch(const uint8_t* xq, const void* xs, const uint8_t* 
         if (int s2 = check_launch("gemm_f16_fused")) return s2;
         if (up.mode != 0) {
             const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - up.full_tiles));
-            tail_sum_kernel<false><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, (int)((M + 2 * FM - 1) / (2 * FM)), 0, up);
+            tail_sum_kernel<false, 2 * FM><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, (int)((M + 2 * FM - 1) / (2 * FM)), 0, up);
             return check_launch("tail_sum");
         }
         return WUSH_OK;
     }
-    gemm_f16_fused_kernel<<<(int)std::min<int64_t>(tiles, sm_count()), Q_THREADS, Q_TOTAL, st>>>(
-        ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N, (int)K, err);
-    return check_launch("gemm_f16_fused");
+    const UnitPlan up = plan_units(tiles, (int)(K / 64), part_room && aligned16(y), 4, 0.81, 0.07);
+    const int64_t units = up.mode == 2 ? sm_count() : up.full_tiles + (up.mode == 1 ? (tiles - up.full_tiles) * up.split : 0);
+    gemm_f16_fused_kernel<<<(int)std::min<int64_t>(units, sm_count()), Q_THREADS, Q_TOTAL, st>>>(
+        ma, mp, (const unsigned short*)ws, dn, sc, (__half*)y, (int)M, (int)N, (int)K, err, up, part);
+    if (int s2 = check_launch("gemm_f16_fused")) return s2;
+    if (up.mode != 0) {
+        const dim3 grid(FM * FN / 8 / 256, (unsigned)(tiles - up.full_tiles));
+        tail_sum_kernel<false, FM><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, (int)((M + FM - 1) / FM), 0, up);
+        return check_launch("tail_sum");
+    }
+    return WUSH_OK;
 }
 
 template <bool I8>
@@ -1111,7 +1134,7 @@ static int launch_tile2(const CUtensorMap& ma, const CUtensorMap& mb, const Tile
     if (int s = check_launch("gemm_tile2")) return s;
     if (up.mode != 0) {
         const dim3 grid((2 * FM) * FN / 8 / 256, (unsigned)(tiles - up.full_tiles));
-        tail_sum_kernel<I8><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, tiles_m, tile_n_first, up);
+        tail_sum_kernel<I8, 2 * FM><<<grid, 256, 0, st>>>(part, sc, (__half*)y, (int)M, (int)N, tiles_m, tile_n_first, up);
         return check_launch("tail_sum");
     }
     return WUSH_OK;
