@@ -118,8 +118,12 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  *   WUSH_GEMM_TILE_F16 : scales folded into exactly-representable fp16 operands, tcgen05
  *                        kind::f16 with fp32 accumulation over the whole K (any M; the fast
  *                        route for prefill; scratch = an fp16 copy of the activations,
- *                        beyond 2048 rows one of the weights, and on layers with few
- *                        output tiles fp32 partial results of a split of K)
+ *                        beyond 2048 rows one of the weights, and room for the fp32 pieces
+ *                        of output tiles that are cut along K -- all tiles of a layer with
+ *                        few of them, else those of the last, partly filled wave of tiles:
+ *                        256 KB per piece, at most two per multiprocessor.  A scratch
+ *                        that holds the copies but not those pieces is accepted; the
+ *                        product then runs without the cut)
  * K % 32 == 0.  Ask wush_w4a4_gemm_workspace_bytes() with the SAME variant for the scratch
  * size; `workspace` may be NULL when it returns 0.  Word 0 of the scratch is an error word:
  * non-zero after the call completes means a bounded wait inside the kernel gave up.
