@@ -274,6 +274,24 @@ int wush_comm_gemv_allgather(void* comm, const uint8_t* xq, const void* xs, cons
 int wush_comm_error(void* comm, int* error);
 int wush_comm_destroy(void* comm);
 
+/* ---- Check of the work split of the persistent tile kernels (host only, no GPU) ----
+ * No counterpart in the reference.  The tile kernels cut the tiles of their last, partly filled
+ * wave along K (wush_w4a4_gemm above); this walks the resulting units exactly as the kernels' CTAs
+ * and the summing kernel do, on the host, for a grid of `workers` CTAs.
+ *   tiles, k_steps   output tiles of the launch and pipeline stages per tile;
+ *   gran             bounds of K ranges are multiples of this many stages;
+ *   force_mode       -1: the split the cost estimate picks for (step_us, piece_us);
+ *                    1: equal K ranges; 2: contiguous runs of stages per CTA (either only if the
+ *                    shape admits it, else no cut);
+ *   cover            [tiles * k_steps] ints out: how many units cover each stage of each tile;
+ *   slots            capacity of the scratch area in 256 x 256 fp32 pieces;
+ *   plan_out         [7] ints out: n_tiles, k_steps, full_tiles, mode, split, ctas, gran.
+ * Returns WUSH_OK if every unit is in range, every piece a CTA writes has its own slot below
+ * `slots` and the summing kernel adds exactly the written pieces of each cut tile, once each;
+ * 101..107, one per broken property, otherwise. */
+int wush_debug_unit_cover(int64_t tiles, int k_steps, int gran, int workers, int force_mode,
+                          double step_us, double piece_us, int* cover, int slots, int* plan_out);
+
 #ifdef __cplusplus
 }
 #endif

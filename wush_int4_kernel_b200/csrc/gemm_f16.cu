@@ -32,6 +32,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -135,14 +136,14 @@ constexpr int F_ACC = 2;                                        // TMEM accumula
 struct UnitPlan { int n_tiles, k_steps, full_tiles, mode, split, ctas, gran; };
 struct Unit { int tile, ks0, len, slot; };                        // slot < 0: a whole tile
 
-__device__ __forceinline__ int unit_count(const UnitPlan& p) {
+__host__ __device__ __forceinline__ int unit_count(const UnitPlan& p) {
     return p.full_tiles + (p.mode == 1 ? (p.n_tiles - p.full_tiles) * p.split : p.mode == 2 ? 2 * p.ctas : 0);
 }
-__device__ __forceinline__ int run_bound(const UnitPlan& p, int c) {           // first stage of CTA c's run (c = ctas: the end)
+__host__ __device__ __forceinline__ int run_bound(const UnitPlan& p, int c) {  // first stage of CTA c's run (c = ctas: the end)
     const long long wg = (long long)(p.n_tiles - p.full_tiles) * p.k_steps / p.gran;
     return (int)(wg * c / p.ctas) * p.gran;
 }
-__device__ __forceinline__ Unit decode_unit(const UnitPlan& p, int u) {
+__host__ __device__ __forceinline__ Unit decode_unit(const UnitPlan& p, int u) {
     if (u < p.full_tiles) return {u, 0, p.k_steps, -1};
     const int v = u - p.full_tiles;
     if (p.mode == 1) {
@@ -151,9 +152,31 @@ __device__ __forceinline__ Unit decode_unit(const UnitPlan& p, int u) {
     }
     const int j = v / p.ctas, c = v - j * p.ctas;
     const int lo = run_bound(p, c), hi = run_bound(p, c + 1);
-    const int tt = lo / p.k_steps, first_end = min(hi, (tt + 1) * p.k_steps);
+    const int tt = lo / p.k_steps, first_end = hi < (tt + 1) * p.k_steps ? hi : (tt + 1) * p.k_steps;
     if (j == 0) return {p.full_tiles + tt, lo - tt * p.k_steps, first_end - lo, c};
     return {p.full_tiles + tt + 1, 0, hi - first_end, p.ctas + tt + 1};
+}
+
+// The slots that hold the pieces of cut tile `tt` (index among the cut tiles), in the order in which they are added:
+// calls add(slot) for each.  The counterpart of decode_unit for tail_sum_kernel.
+template <typename F>
+__host__ __device__ __forceinline__ void pieces_of_tile(const UnitPlan& plan, int tt, F&& add) {
+    if (plan.mode == 1) {
+        for (int r = 0; r < plan.split; ++r) add(tt * plan.split + r);
+        return;
+    }
+    // mode 2: the run that contains the tile's first stage, then every run that starts inside the tile
+    const int tb = tt * plan.k_steps, te = tb + plan.k_steps;
+    const long long wg = (long long)(plan.n_tiles - plan.full_tiles) * plan.k_steps / plan.gran;
+    int c = (int)((long long)(tb / plan.gran) * plan.ctas / wg);
+    while (c > 0 && run_bound(plan, c) > tb) --c;
+    while (c + 1 < plan.ctas && run_bound(plan, c + 1) <= tb) ++c;          // now bound(c) <= tb < bound(c + 1), or c is the last run
+    if (run_bound(plan, c) < tb) {
+        if (run_bound(plan, c + 1) > tb) add(plan.ctas + tt);               // second piece of run c: the start of this tile
+        ++c;
+    }
+    for (; c < plan.ctas && run_bound(plan, c) < te; ++c)
+        if (run_bound(plan, c + 1) > run_bound(plan, c)) add(c);            // first piece of run c
 }
 
 // K-major operand in the 128-byte-swizzled layout TMA writes: rows of 128 B, 8-row groups 1 KB apart.
@@ -904,22 +927,7 @@ tail_sum_kernel(const float* __restrict__ part, const TileScale sc, __half* __re
             else acc[q] += f[q];
         }
     };
-    if (plan.mode == 1) {
-        for (int r = 0; r < plan.split; ++r) add(tt * plan.split + r);
-    } else {
-        // the run that contains the tile's first stage, then every run that starts inside the tile
-        const int tb = tt * plan.k_steps, te = tb + plan.k_steps;
-        const long long wg = (long long)(plan.n_tiles - plan.full_tiles) * plan.k_steps / plan.gran;
-        int c = (int)((long long)(tb / plan.gran) * plan.ctas / wg);
-        while (c > 0 && run_bound(plan, c) > tb) --c;
-        while (c + 1 < plan.ctas && run_bound(plan, c + 1) <= tb) ++c;      // now bound(c) <= tb < bound(c + 1), or c is the last run
-        if (run_bound(plan, c) < tb) {
-            if (run_bound(plan, c + 1) > tb) add(plan.ctas + tt);           // second piece of run c: the start of this tile
-            ++c;
-        }
-        for (; c < plan.ctas && run_bound(plan, c) < te; ++c)
-            if (run_bound(plan, c + 1) > run_bound(plan, c)) add(c);        // first piece of run c
-    }
+    pieces_of_tile(plan, tt, add);
     float fs[8];
     float fm;
     if constexpr (I8) {
@@ -1039,12 +1047,14 @@ size_t f16_workspace_bytes(int64_t M, int64_t N, int64_t K)
 // that -- by dealing their stages to all CTAs as contiguous runs (mode 2); tail_sum_kernel adds the pieces.
 // The choice is by estimate: rounds of stages at `step_us` each, plus what the fp32 pieces cost (measured:
 // about 0.13 us per 256 x 256 piece written and read back, 5 us for the summing kernel), against one whole round.
-static UnitPlan plan_units(int64_t tiles, int k_steps, bool room, int gran, double step_us, double piece_us = 0.13)
+// `workers` = CTAs of the grid; 0 = one per SM of the current device.
+static UnitPlan plan_units(int64_t tiles, int k_steps, bool room, int gran, double step_us, double piece_us = 0.13,
+                           int workers = 0)
 {
-    UnitPlan p = {(int)tiles, k_steps, (int)tiles, 0, 1, sm_count(), gran};
+    const int sms = workers > 0 ? workers : sm_count();
+    UnitPlan p = {(int)tiles, k_steps, (int)tiles, 0, 1, sms, gran};
     const char* v = std::getenv("WUSH_TAIL_SPLIT");                    // 0: never cut; 1 / 2: only that mode (measurements, tests)
     if (!room || (v && v[0] == '0')) return p;
-    const int sms = sm_count();
     const int full = (int)(tiles / sms) * sms, tail = (int)tiles - full;
     if (tail == 0) return p;
     double best = k_steps * step_us;                                   // the last wave as it is
@@ -1421,4 +1431,66 @@ WUSH_API int wush_w4a4_gemm_static_scratch(const uint8_t* xq, const void* xs, co
     // size against the route it really takes (a scale pointer that is not 16-byte aligned needs room for
     // an fp16 copy of the weights) before anything is launched.
     return f16_dispatch(xq, xs, wq, ws, M, N, K, y, scratch, (size_t)WUSH_STATIC_SCRATCH_BYTES, (cudaStream_t)stream, err);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host-side check of the unit plans (no counterpart in the reference; used by the CPU test suite)
+// ------------------------------------------------------------------------------------------------
+// Walks the units exactly as the tile kernels do (CTA b takes units b, b + workers, ...) and the pieces exactly as
+// tail_sum_kernel does.  cover[tile * k_steps + k] receives how many units cover stage k of the tile;
+// returns 0 (else 101..107, one per property) if, besides, every piece a kernel writes for a cut tile is added exactly once by the summing kernel,
+// every slot is below `slots` and written once, and (mode 2) unit u is met by CTA u mod workers = its run.
+// `tiles` / `k_steps` / `gran` / `workers` as for plan_units; force_mode: -1 = take plan_units' choice for the given
+// cost figures, else 1 or 2 with the plan built the same way.  plan_out (7 ints) receives the plan.
+WUSH_API int wush_debug_unit_cover(int64_t tiles, int k_steps, int gran, int workers, int force_mode, double step_us,
+                                   double piece_us, int* cover, int slots, int* plan_out)
+{
+    using namespace wush;
+    if (tiles <= 0 || k_steps <= 0 || gran <= 0 || workers <= 0 || !cover || !plan_out)
+        return fail(WUSH_ERR_INVALID_ARGUMENT, "debug_unit_cover: bad argument");
+    UnitPlan p = {(int)tiles, k_steps, (int)tiles, 0, 1, workers, gran};
+    {
+        const int full = (int)(tiles / workers) * workers, tail = (int)tiles - full;
+        if (force_mode < 0) {
+            p = plan_units(tiles, k_steps, true, gran, step_us, piece_us, workers);
+        } else if (tail > 0 && force_mode == 1) {
+            int r = 1;
+            while (tail * r * 2 <= workers && k_steps % (r * 2) == 0 && k_steps / (r * 2) >= 4 && (k_steps / (r * 2)) % gran == 0) r *= 2;
+            if (r > 1) { p.full_tiles = full; p.mode = 1; p.split = r; }
+        } else if (tail > 0 && force_mode == 2 && k_steps % gran == 0 && (long long)tail * k_steps / gran >= workers) {
+            p.full_tiles = full; p.mode = 2;
+        }
+    }
+    const int fields[7] = {p.n_tiles, p.k_steps, p.full_tiles, p.mode, p.split, p.ctas, p.gran};
+    for (int i = 0; i < 7; ++i) plan_out[i] = fields[i];
+    for (int64_t i = 0; i < tiles * k_steps; ++i) cover[i] = 0;
+    std::vector<int> slot_tile((size_t)slots, -1);
+    const int n_units = unit_count(p);
+    const int grid = p.mode == 2 ? workers : std::min(n_units, workers);
+    for (int b = 0; b < grid; ++b) {
+        for (int u = b; u < n_units; u += grid) {
+            const Unit un = decode_unit(p, u);
+            if (un.len == 0) continue;
+            if (un.tile < 0 || un.tile >= p.n_tiles || un.ks0 < 0 || un.ks0 + un.len > p.k_steps) return 101;
+            if (un.ks0 % gran != 0) return 102;
+            for (int k = un.ks0; k < un.ks0 + un.len; ++k) ++cover[(int64_t)un.tile * k_steps + k];
+            if (un.slot < 0) { if (un.tile >= p.full_tiles) return 103; continue; }
+            if (un.tile < p.full_tiles || un.slot >= slots || slot_tile[un.slot] != -1) return 104;
+            slot_tile[un.slot] = un.tile;
+            if (p.mode == 2 && (u - p.full_tiles) % p.ctas != b) return 105;
+        }
+    }
+    if (p.mode != 0) {
+        std::vector<int> added((size_t)slots, 0);
+        for (int tt = 0; tt < p.n_tiles - p.full_tiles; ++tt) {
+            int bad = 0;
+            pieces_of_tile(p, tt, [&](int slot) {
+                if (slot < 0 || slot >= slots || slot_tile[slot] != p.full_tiles + tt || added[slot]++) bad = 1;
+            });
+            if (bad) return 106;
+        }
+        for (int sl = 0; sl < slots; ++sl)
+            if ((slot_tile[sl] != -1) != (added[sl] == 1)) return 107;
+    }
+    return 0;
 }
