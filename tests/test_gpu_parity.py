@@ -312,12 +312,13 @@ def test_decode_tcgen05_needs_scratch(dev):
 
 
 def test_auto_variant_by_shape(dev):
-    """What AUTO stands for: the GEMV for one or two rows, the streaming kernel for decode batches and for
+    """What AUTO stands for: the GEMV for up to three rows (four on all but the widest layers), the streaming kernel for decode batches and for
     mid-size M on narrow layers, the fp16 route where its tiles (or K ranges) fill the machine."""
     lib = capi.load()
     pick = lib.wush_w4a4_gemm_pick_variant
     assert pick(1, 57344, 8192) == capi.GEMM_GEMV and pick(2, 8192, 8192) == capi.GEMM_GEMV
     assert pick(4, 57344, 8192) == capi.GEMM_DECODE and pick(4, 8192, 8192) == capi.GEMM_GEMV
+    assert pick(3, 57344, 8192) == capi.GEMM_GEMV and pick(4, 24576, 4096) == capi.GEMM_GEMV
     assert pick(16, 57344, 8192) == capi.GEMM_DECODE and pick(32, 24576, 4096) == capi.GEMM_DECODE
     assert pick(64, 8192, 8192) == capi.GEMM_DECODE and pick(128, 8192, 3584) == capi.GEMM_DECODE
     assert pick(128, 57344, 8192) == capi.GEMM_TILE_F16 and pick(256, 8192, 8192) == capi.GEMM_TILE_F16
@@ -374,6 +375,24 @@ def test_gemm_every_variant(dev, orc):
             _assert_close(cabi.gemm(*d, variant=v), y64, (M, N, K, v))
     with pytest.raises(capi.WushError):
         cabi.gemm(*_to_dev(dev, *_operands(8, 16, 64, 1, orc)), variant=capi.GEMM_GEMV)
+
+
+@pytest.mark.parametrize("shape", [(1, 77, 8192), (2, 130, 8192), (3, 67, 28672), (4, 50, 2048), (2, 33, 1024), (3, 20, 4096),
+                                   (4, 9, 320), (1, 5, 12288)], ids=lambda s: "x".join(map(str, s)))
+def test_gemv_rows_per_trip(dev, orc, shape, monkeypatch):
+    """The GEMV takes two or four weight rows per trip and reloads a slot as soon as it is consumed: rows that
+    end inside a unit, rows of one, several and a fractional number of trips, and both row counts -- which add
+    every row's groups in the same order, so their results are the same bits."""
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=3 * M + N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    d = _to_dev(dev, *ops)
+    ys = []
+    for rows in ("2", "4"):
+        monkeypatch.setenv("WUSH_GEMV_ROWS", rows)
+        ys.append(cabi.gemm(*d, variant=capi.GEMM_GEMV))
+        _assert_close(ys[-1], y64, (shape, rows))
+    assert torch.equal(ys[0], ys[1])
 
 
 def test_gemm_golden(dev, orc, golden):

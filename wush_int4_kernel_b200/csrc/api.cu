@@ -112,9 +112,10 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
 {
     if (variant != WUSH_GEMM_AUTO) return variant;
     const bool gemv_ok = gemv_smem_bytes((int)(M < 4 ? M : 4), K) <= 200 * 1024;
-    // three or four rows: the tensor-core streaming kernel wins on wide layers, the CUDA-core GEMV on narrow
-    // ones (a CTA of the streaming kernel is left with one or two warps there)
-    if (M <= 4 && gemv_ok && (M <= 2 || K % 256 != 0 || N <= 16384)) return WUSH_GEMM_GEMV;
+    // Up to three rows the CUDA-core GEMV is ahead everywhere (K = 8192, N = 57344: 38 / 39 / 48 us at M = 1 / 2 / 3
+    // against 54 us of the streaming kernel); at four rows it is on all but the widest layers (that one: 56 against
+    // 54 us; K = 4096, N = 24576: 16.7 against 19.5 us).
+    if (M <= 4 && gemv_ok && (M <= 3 || K % 256 != 0 || N <= 32768)) return WUSH_GEMM_GEMV;
     // Up to 32 rows: the streaming kernel.  The tcgen05 kernel with swapped operands (DECODE_TC) computes the same
     // product but is slower on every shape measured so far (K = 8192, N = 57344: 93 / 96 / 139 us against 55 / 77 /
     // 119 us at M = 8 / 16 / 32), so AUTO never picks it.

@@ -9,29 +9,38 @@
 //   * a CTA first expands the M activation rows into shared memory as signed bytes
 //     (16 * code, even and odd codes of a group in separate 16-byte vectors, so lanes read
 //     consecutive vectors without bank conflicts) and their scales as fp32 / 256;
-//   * each warp owns one weight row per trip; lane l takes groups l, l+32, ...: one 16-byte
-//     load of codes and one 2-byte load of the scale per group, eight groups (144 B per lane)
-//     in flight before the first use; the next row's loads are issued before the reduction
-//     of the current one, and the very first ones before the activation prologue;
+//   * each warp owns two weight rows per trip (four on short rows, K <= 2048, under several activation rows);
+//     lane l takes groups l, l+32, ... of each: one 16-byte load of codes and one 2-byte load of the scale per
+//     group and row, eight of them (144 B per lane) in flight at any time: a slot is loaded again -- for the next
+//     trip of the unit, or the first trip of the warp's next unit -- as soon as its words have been widened;
+//     the very first loads go out before the activation prologue;
 //   * a word of 8 nibbles becomes two words of 4 signed bytes with one shift and two ANDs
-//     (byte = 16 * code, no sign extension needed), then dp4a against the activation bytes:
-//     the exact group sum comes out multiplied by 256, which the pre-scaled sx undoes;
+//     (byte = 16 * code, no sign extension needed), then dp4a against the activation bytes, which are read from
+//     shared memory once for all rows of the trip (with M rows of activations every weight row would otherwise
+//     cost a pass over M * K bytes of shared memory -- at M >= 2 more than the multiprocessor can deliver in
+//     the time the weights take to arrive);
+//   * the dot product accumulates onto the bit pattern of 1.5 * 2^23, so that read as fp32 it is
+//     12582912 + 256 * P_g and fma(f, sw, -12582912 * sw) = 256 * P_g * sw exactly: no integer -> float
+//     conversion; the pre-scaled sx undoes the 256;
 //   * fp32 accumulation over groups per lane, xor-shuffle tree over lanes, fp16 store.
 //
-// Short rows (K <= 4096) are taken two or four at a time so that a lane still has eight loads
-// in flight.  The grid is persistent (every CTA resident) and the units are dealt round-robin to
+// The grid is persistent (every CTA resident) and the units are dealt round-robin to
 // the warps; when the whole job is only a few rounds long, the number of warps per CTA and of
 // CTAs per multiprocessor is chosen so that the rounds come out full.
 // The kernel is launched as a programmatic dependent of the kernel before it (normally the
 // fused transform+quantisation): it gets resident and prefetches while that kernel drains, and
 // reads the activations only after griddepcontrol.wait.
 // Algorithmic HBM bytes per call: 9*N*K/16 (codes + scales of W) + 9*M*K/16 + 2*M*N.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "peer_common.cuh"
 
 namespace wush {
 
 constexpr int GV_MAX_WARPS = 8;
+constexpr uint32_t GV_MAGIC_BITS = 0x4B400000u;          // 1.5 * 2^23 as fp32
+constexpr float GV_MAGIC = 12582912.0f;
 
 // The loads of one trip of one warp: 8 slots of 16 bytes of codes + one scale per lane (144 B
 // in flight per lane).  A trip covers R weight rows; row r of the unit owns slots
@@ -41,40 +50,54 @@ struct RowLoads {
     unsigned short s[8];
 };
 
+// Where the R rows of a trip start for this lane (group gb + lane of each row) and which of them exist.
 template <int R>
-__device__ __forceinline__ void issue_unit_loads(RowLoads& r, const uint8_t* __restrict__ wq,
-                                                 const unsigned short* __restrict__ ws16, int unit, int gb, int lane,
-                                                 int G, int N, size_t K2)
+struct TripBase {
+    const uint8_t* wp[R];
+    const unsigned short* sp[R];
+    int g0;
+    bool live[R];
+};
+
+template <int R>
+__device__ __forceinline__ TripBase<R> trip_base(const uint8_t* __restrict__ wq, const unsigned short* __restrict__ ws16,
+                                                 int unit, int gb, int lane, int G, int N, size_t K2, bool any)
+{
+    TripBase<R> t;
+    t.g0 = gb + lane;
+#pragma unroll
+    for (int rr = 0; rr < R; ++rr) {
+        const int row = unit * R + rr;
+        t.live[rr] = any && row < N;
+        t.wp[rr] = wq + (size_t)(t.live[rr] ? row : 0) * K2 + (size_t)t.g0 * 16;
+        t.sp[rr] = ws16 + (size_t)(t.live[rr] ? row : 0) * G + t.g0;
+    }
+    return t;
+}
+
+// Slot u of every row of the trip: group g0 + 32 u.
+template <int R>
+__device__ __forceinline__ void issue_slot_loads(RowLoads& r, const TripBase<R>& t, int u, int G)
 {
     constexpr int U = 8 / R;
 #pragma unroll
     for (int rr = 0; rr < R; ++rr) {
-        const int row = unit * R + rr;
-        const bool live = row < N;
-        const int g0 = gb + lane;
-        // one base address per row; the U slots sit at fixed offsets from it
-        const uint8_t* wp = wq + (size_t)(live ? row : 0) * K2 + (size_t)g0 * 16;
-        const unsigned short* sp = ws16 + (size_t)(live ? row : 0) * G + g0;
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (live && g0 + u * 32 < G) {
-                r.w[rr * U + u] = ldg_nc_v4(wp + u * 512);
-                r.s[rr * U + u] = __ldg(sp + u * 32);
-            } else {
-                r.w[rr * U + u] = make_uint4(0, 0, 0, 0);
-                r.s[rr * U + u] = 0;
-            }
+        if (t.live[rr] && t.g0 + u * 32 < G) {
+            r.w[rr * U + u] = ldg_nc_v4(t.wp[rr] + u * 512);
+            r.s[rr * U + u] = __ldg(t.sp[rr] + u * 32);
+        } else {
+            r.w[rr * U + u] = make_uint4(0, 0, 0, 0);
+            r.s[rr * U + u] = 0;
         }
     }
 }
 
-// R = weight rows per warp and trip.  R > 1 is used when a row has at most 32 * (8/R) groups,
-// so that short rows still put 8 loads per lane in flight; a trip is then a whole unit.
+// R = weight rows per warp and trip (2 or 4): a trip is 32 * (8/R) groups of each.
 // PUSH: instead of y the result goes into slot (step & 1, rank) of EVERY rank's exchange buffer
 // (remote stores over NVLink from the epilogue); when the last CTA is done it publishes the step
 // to all ranks.  The sum over ranks is then a purely local read (peer_reduce.cu).
 template <int MB, int R, bool PUSH>
-__global__ void __launch_bounds__(GV_MAX_WARPS * 32)
+__global__ void __launch_bounds__(GV_MAX_WARPS * 32, MB == 1 ? 3 : 2)
 gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
                  const __nv_bfloat16* __restrict__ xs,     // (MB, G)
                  const uint8_t* __restrict__ wq,           // (N, K/2)
@@ -109,7 +132,11 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
 
     // start the weight stream first: it does not depend on the shared-memory prologue
     RowLoads cur;
-    if (unit < units) issue_unit_loads<R>(cur, wq, ws16, unit, 0, lane, G, N, K2);
+    {
+        const TripBase<R> first = trip_base<R>(wq, ws16, unit, 0, lane, G, N, K2, unit < units);
+#pragma unroll
+        for (int u = 0; u < U; ++u) issue_slot_loads<R>(cur, first, u, G);
+    }
 
     for (int idx = threadIdx.x; idx < MB * G; idx += blockDim.x) {
         uint4 w = *reinterpret_cast<const uint4*>(xq + (size_t)idx * 4);
@@ -128,60 +155,83 @@ gemv_dp4a_kernel(const uint32_t* __restrict__ xq,          // (MB, K/8) words
         push_off = slot_offset(peers, step, peers.rank);
     }
 
-    for (; unit < units; unit += stride) {
-        float acc[R][MB];
+    // The work of a warp is a sequence of trips: 32 * U groups of R rows each, unit after unit.  A slot is loaded
+    // again, for the NEXT trip, as soon as its words have been widened, so the lane keeps 8 loads in flight all the
+    // time -- across trips of a unit and across units alike.
+    float acc[R][MB];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
-        for (int gb = 0; gb < G; gb += 32 * U) {
-            if (gb) issue_unit_loads<R>(cur, wq, ws16, unit, gb, lane, G, N, K2);
+        for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+    int gb = 0;
+    while (unit < units) {
+        int n_unit = unit, n_gb = gb + 32 * U;
+        if (n_gb >= G) { n_gb = 0; n_unit = unit + stride; }
+        const TripBase<R> nxt = trip_base<R>(wq, ws16, n_unit, n_gb, lane, G, N, K2, n_unit < units);
 #pragma unroll
-            for (int slot = 0; slot < 8; ++slot) {
-                const int g = min(gb + (slot % U) * 32 + lane, G - 1);  // lanes past the end carry zero weights
-                uint4 ae, ao;
-                unpack_x16(cur.w[slot].x, ae.x, ao.x); unpack_x16(cur.w[slot].y, ae.y, ao.y);
-                unpack_x16(cur.w[slot].z, ae.z, ao.z); unpack_x16(cur.w[slot].w, ae.w, ao.w);
-                const float sw = bf16_bits_to_f32(cur.s[slot]);
+        for (int u = 0; u < U; ++u) {
+            const int g = min(gb + u * 32 + lane, G - 1);               // lanes past the end carry zero weights
+            // the R rows' words of this group, widened once; then every activation row is read once for all of them
+            uint4 ae[R], ao[R];
+            float sw[R], csw[R];
 #pragma unroll
-                for (int m = 0; m < MB; ++m) {
-                    const uint4 ve = xe[m * G + g], vo = xo[m * G + g];
-                    int d = dp4a_s8(ae.x, ve.x, 0); d = dp4a_s8(ao.x, vo.x, d);
-                    d = dp4a_s8(ae.y, ve.y, d); d = dp4a_s8(ao.y, vo.y, d);
-                    d = dp4a_s8(ae.z, ve.z, d); d = dp4a_s8(ao.z, vo.z, d);
-                    d = dp4a_s8(ae.w, ve.w, d); d = dp4a_s8(ao.w, vo.w, d);
-                    acc[slot / U][m] = fmaf((float)d, sxf[m * G + g] * sw, acc[slot / U][m]);
+            for (int r = 0; r < R; ++r) {
+                const uint4 w = cur.w[r * U + u];
+                unpack_x16(w.x, ae[r].x, ao[r].x); unpack_x16(w.y, ae[r].y, ao[r].y);
+                unpack_x16(w.z, ae[r].z, ao[r].z); unpack_x16(w.w, ae[r].w, ao[r].w);
+                sw[r] = bf16_bits_to_f32(cur.s[r * U + u]);
+                csw[r] = -GV_MAGIC * sw[r];                              // exact: 2 x 8 significant bits
+            }
+            issue_slot_loads<R>(cur, nxt, u, G);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                const uint4 ve = xe[m * G + g], vo = xo[m * G + g];
+                const float sx = sxf[m * G + g];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    // the sum starts from the bits of 1.5 * 2^23: read as fp32 it is 12582912 + 256 * P_g, and
+                    // fma(f, sw, -12582912 * sw) = 256 * P_g * sw exactly -- no integer -> float conversion
+                    int d = dp4a_s8(ae[r].x, ve.x, (int)GV_MAGIC_BITS); d = dp4a_s8(ao[r].x, vo.x, d);
+                    d = dp4a_s8(ae[r].y, ve.y, d); d = dp4a_s8(ao[r].y, vo.y, d);
+                    d = dp4a_s8(ae[r].z, ve.z, d); d = dp4a_s8(ao[r].z, vo.z, d);
+                    d = dp4a_s8(ae[r].w, ve.w, d); d = dp4a_s8(ao[r].w, vo.w, d);
+                    acc[r][m] = fmaf(fmaf(__int_as_float(d), sw[r], csw[r]), sx, acc[r][m]);
                 }
             }
         }
-        // next unit's first trip goes out before the reduction of this one
-        const int next = unit + stride;
-        if (next < units) issue_unit_loads<R>(cur, wq, ws16, next, 0, lane, G, N, K2);
+        if (n_gb == 0) {                                                 // the unit is complete
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+            for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
+                for (int m = 0; m < MB; ++m) {
 #pragma unroll
-                for (int off = 16; off; off >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], off);
-            }
-        if (lane == 0) {
+                    for (int off = 16; off; off >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], off);
+                }
+            if (lane == 0) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int n = unit * R + r;
-                if (n < N) {
+                for (int r = 0; r < R; ++r) {
+                    const int n = unit * R + r;
+                    if (n < N) {
 #pragma unroll
-                    for (int m = 0; m < MB; ++m) {
-                        const __half h = __float2half_rn(acc[r][m]);
-                        if constexpr (PUSH) {
-                            for (int p = 0; p < peers.world; ++p)
-                                reinterpret_cast<__half*>(peers.base[p] + push_off)[(size_t)m * N + n] = h;
-                        } else {
-                            y[(size_t)m * N + n] = h;
+                        for (int m = 0; m < MB; ++m) {
+                            const __half h = __float2half_rn(acc[r][m]);
+                            if constexpr (PUSH) {
+                                for (int p = 0; p < peers.world; ++p)
+                                    reinterpret_cast<__half*>(peers.base[p] + push_off)[(size_t)m * N + n] = h;
+                            } else {
+                                y[(size_t)m * N + n] = h;
+                            }
                         }
                     }
                 }
             }
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
         }
+        unit = n_unit;
+        gb = n_gb;
     }
     if constexpr (PUSH) {
         __threadfence_system();                            // this thread's remote stores are ordered before the flag
@@ -271,24 +321,28 @@ static cudaError_t set_attr()
 int gemv_set_attributes()
 {
     cudaError_t e;
-    if ((e = set_attr<1, 1>()) != cudaSuccess || (e = set_attr<1, 2>()) != cudaSuccess || (e = set_attr<1, 4>()) != cudaSuccess ||
-        (e = set_attr<2, 1>()) != cudaSuccess || (e = set_attr<2, 2>()) != cudaSuccess || (e = set_attr<2, 4>()) != cudaSuccess ||
-        (e = set_attr<3, 1>()) != cudaSuccess || (e = set_attr<3, 2>()) != cudaSuccess ||
-        (e = set_attr<4, 1>()) != cudaSuccess || (e = set_attr<4, 2>()) != cudaSuccess)
+    if ((e = set_attr<1, 2>()) != cudaSuccess || (e = set_attr<1, 4>()) != cudaSuccess ||
+        (e = set_attr<2, 2>()) != cudaSuccess || (e = set_attr<2, 4>()) != cudaSuccess ||
+        (e = set_attr<3, 2>()) != cudaSuccess || (e = set_attr<3, 4>()) != cudaSuccess ||
+        (e = set_attr<4, 2>()) != cudaSuccess || (e = set_attr<4, 4>()) != cudaSuccess)
         return fail(WUSH_ERR_CUDA, "gemv: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
 
+// Rows per warp and trip, from measurements at M = 1..4 on K x N = 1024 x 4096, 2048 x 8192, 4096 x 24576,
+// 8192 x 7168, 8192 x 57344 and 28672 x 8192: two rows everywhere, except four on short rows (a lane's 8 loads
+// then cover the whole row) under two or more activation rows.  WUSH_GEMV_ROWS=2|4 overrides (measurements).
 template <int MB, bool PUSH>
 static int launch_rows(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t N, int64_t K,
                        void* y, const PeerTable& peers, cudaStream_t st)
 {
     const int64_t slots = (K / 32 + 31) / 32;              // 16-byte loads per lane and row
-    if constexpr (MB <= 2) {
-        if (slots <= 2) return launch_gemv<MB, 4, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
+    int rows = (MB >= 2 && slots <= 2) ? 4 : 2;
+    if (const char* v = std::getenv("WUSH_GEMV_ROWS")) {
+        if (v[0] == '2' || v[0] == '4') rows = v[0] - '0';
     }
-    if (slots <= 4) return launch_gemv<MB, 2, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
-    return launch_gemv<MB, 1, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
+    if (rows == 4) return launch_gemv<MB, 4, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
+    return launch_gemv<MB, 2, PUSH>(xq, xs, wq, ws, N, K, y, peers, st);
 }
 
 // M in 1..4, shared memory must fit (checked by the dispatcher).
