@@ -101,7 +101,7 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  * Replaces w4a4_gemm_s4 (csrc/gemm_s4.cu:320-379), w4a4_gemm / _v1 / _v2
  * (csrc/gemm_int4.cu:89-130, csrc/gemm_wmma.cu:128-172, csrc/gemm_wmma2.cu:141-181),
  * w4a4_gemv and w4a4_gemv_multi (csrc/gemv_int4.cu:145-223).
- *   WUSH_GEMM_AUTO     : pick by shape (GEMV for M <= 2, and for M <= 4 on narrow layers;
+ *   WUSH_GEMM_AUTO     : pick by shape (GEMV for M <= 3, and for M = 4 unless N > 32768;
  *                        DECODE up to 32 rows; for 32 < M <= 512 the cheaper of DECODE in
  *                        32-row blocks and TILE_F16 by a measured cost estimate in N, K and
  *                        M; TILE_F16 beyond; the exact-sum TILE variant only on request)
