@@ -114,6 +114,11 @@ int wush_fused_silu_mul_transform_quant_int4(const void* gate_up, const void* t,
  *                        K % 256 == 0, M <= 32, scales 16-byte aligned.  Same results as DECODE to
  *                        fp32 summation order; measured slower than DECODE on this part, so AUTO
  *                        never picks it (kept as the exact tcgen05 reference of the decode path)
+ *   WUSH_GEMM_GEMV_MMA : the weights streamed from global memory straight into mma.sync
+ *                        fragments, every lane its own ring of asynchronous copies, no
+ *                        barriers (1 <= M <= 16, K % 128 == 0, the widened activations --
+ *                        about 17/16 * K bytes per row, rows rounded up to even -- within
+ *                        about 185 KB of shared memory, scales 4-byte aligned)
  *   WUSH_GEMM_TILE     : tcgen05 kind::i8 tile GEMM, exact int32 sum per group (any M)
  *   WUSH_GEMM_TILE_F16 : scales folded into exactly-representable fp16 operands, tcgen05
  *                        kind::f16 with fp32 accumulation over the whole K (any M; the fast
@@ -139,7 +144,8 @@ typedef enum {
     WUSH_GEMM_DECODE = 2,
     WUSH_GEMM_TILE = 3,
     WUSH_GEMM_TILE_F16 = 4,
-    WUSH_GEMM_DECODE_TC = 5
+    WUSH_GEMM_DECODE_TC = 5,
+    WUSH_GEMM_GEMV_MMA = 6
 } wush_gemm_variant;
 size_t wush_w4a4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int variant);
 /* The variant WUSH_GEMM_AUTO stands for on the current device for this shape (one of the other

@@ -395,6 +395,41 @@ def test_gemv_rows_per_trip(dev, orc, shape, monkeypatch):
     assert torch.equal(ys[0], ys[1])
 
 
+GEMV_MMA_SHAPES = [(1, 16, 512), (2, 77, 128), (3, 130, 1152), (4, 50, 2048), (5, 264, 640), (6, 33, 4096), (7, 1000, 1024),
+                   (8, 264, 8192), (8, 2400, 512), (9, 40, 1024), (12, 520, 2048), (13, 17, 4096), (16, 300, 8192), (16, 5000, 512)]
+
+
+@pytest.mark.parametrize("shape", GEMV_MMA_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_gemv_mma_vs_fp64(dev, orc, shape):
+    """Weights streamed straight into mma.sync fragments (variant GEMV_MMA): every chain count (M = 1..16, odd M
+    padded with a zero row), row blocks that end inside a unit of 16, one to sixteen ring rounds per row, more
+    units than resident warps (several units per warp, loads crossing from one unit to the next)."""
+    M, N, K = shape
+    ops = _operands(M, N, K, seed=5 * M + N, orc=orc)
+    y64 = orc.gemm_f64(*ops)
+    y = cabi.gemm(*_to_dev(dev, *ops), variant=capi.GEMM_GEMV_MMA)
+    _assert_close(y, y64, shape)
+
+
+def test_gemv_mma_exact_against_streaming_kernel(dev, orc):
+    """Group sums are exact integers in both kernels and both apply the scales with the same two FMAs; only the
+    order in which a row's groups are added differs, so the results agree to fp32 summation order -- and zero rows
+    of activations give exact zeros."""
+    M, N, K = 8, 520, 2048
+    xq, xs, wq, ws = _operands(M, N, K, seed=21, orc=orc)
+    xq = xq.copy()
+    xq[3] = 0
+    d = _to_dev(dev, xq, xs, wq, ws)
+    a = cabi.gemm(*d, variant=capi.GEMM_GEMV_MMA).float()
+    b = cabi.gemm(*d, variant=capi.GEMM_DECODE).float()
+    assert (a[3] == 0).all()
+    assert (a - b).abs().max() <= 2e-3 * b.abs().max()
+    with pytest.raises(capi.WushError):
+        cabi.gemm(*_to_dev(dev, *_operands(4, 16, 96, 1, orc)), variant=capi.GEMM_GEMV_MMA)      # K not a multiple of 128
+    with pytest.raises(capi.WushError):
+        cabi.gemm(*_to_dev(dev, *_operands(17, 16, 512, 1, orc)), variant=capi.GEMM_GEMV_MMA)    # more than 16 rows
+
+
 def test_gemm_golden(dev, orc, golden):
     z = golden("w4a4_matmul")
     for (M, N, K) in z["shapes"]:

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_PKG, "libwush_int4_b200.so")
 WUSH_OK = 0
 WUSH_ERR_INVALID_ARGUMENT, WUSH_ERR_CUDA, WUSH_ERR_UNSUPPORTED, WUSH_ERR_WORKSPACE, WUSH_ERR_DEVICE_FLAG = 1, 2, 3, 4, 5
 TQ_EXACT, TQ_FAST = 0, 1
-GEMM_AUTO, GEMM_GEMV, GEMM_DECODE, GEMM_TILE, GEMM_TILE_F16, GEMM_DECODE_TC = 0, 1, 2, 3, 4, 5
+GEMM_AUTO, GEMM_GEMV, GEMM_DECODE, GEMM_TILE, GEMM_TILE_F16, GEMM_DECODE_TC, GEMM_GEMV_MMA = 0, 1, 2, 3, 4, 5, 6
 
 _vp, _i64, _int, _f32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 

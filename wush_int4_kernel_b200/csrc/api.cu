@@ -35,6 +35,7 @@ static int g_ready[MAX_DEVICES];        // 0 = not yet, 1 = ok, <0 = -(status)
 static int g_sms[MAX_DEVICES];
 
 int gemv_set_attributes();
+int gemv_mma_set_attributes();
 int mma_set_attributes();
 int tc_set_attributes();
 int stream_set_attributes();
@@ -51,6 +52,7 @@ static int init_device(int dev)
                     dev, prop.major, prop.minor);
     g_sms[dev] = prop.multiProcessorCount;
     if (int s = gemv_set_attributes()) return s;
+    if (int s = gemv_mma_set_attributes()) return s;
     if (int s = mma_set_attributes()) return s;
     if (int s = tc_set_attributes()) return s;
     if (int s = stream_set_attributes()) return s;
@@ -86,6 +88,8 @@ int sm_count()
 size_t gemv_smem_bytes(int M, int64_t K);
 int gemv_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
 int mma_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
+bool gemv_mma_supported(int64_t M, int64_t N, int64_t K, const void* xs, const void* ws);
+int gemv_mma_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
 bool tc_supported(int64_t M, int64_t N, int64_t K);
 size_t tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int tc_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, void*,
@@ -175,7 +179,7 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
     using namespace wush;
     if (int e = ensure_init()) return e;
     WUSH_REQUIRE(M >= 0 && N >= 0 && K > 0 && K % 32 == 0, "w4a4_gemm: K must be a positive multiple of 32");
-    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_DECODE_TC, "w4a4_gemm: unknown variant %d", variant);
+    WUSH_REQUIRE(variant >= WUSH_GEMM_AUTO && variant <= WUSH_GEMM_GEMV_MMA, "w4a4_gemm: unknown variant %d", variant);
     if (M == 0 || N == 0) return WUSH_OK;
     WUSH_REQUIRE(xq && xs && wq && ws && y, "w4a4_gemm: null pointer");
     WUSH_REQUIRE(aligned16(xq) && aligned16(wq), "w4a4_gemm: packed codes must be 16-byte aligned");
@@ -190,6 +194,12 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
             return gemv_dispatch(xq, xs, wq, ws, M, N, K, y, st);
         case WUSH_GEMM_DECODE:
             return mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
+        case WUSH_GEMM_GEMV_MMA:
+            if (!gemv_mma_supported(M, N, K, xs, ws))
+                return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm: the GEMV_MMA variant takes 1..16 rows, K a multiple of 128 with the "
+                                                  "activations in shared memory, 4-byte aligned scales (M=%lld K=%lld)",
+                            (long long)M, (long long)K);
+            return gemv_mma_dispatch(xq, xs, wq, ws, M, N, K, y, st);
         case WUSH_GEMM_DECODE_TC:
             return decode_tc_dispatch(xq, xs, wq, ws, M, N, K, y, workspace, workspace_bytes, st);
         case WUSH_GEMM_TILE_F16:

@@ -46,7 +46,7 @@ def main(argv):
     elif op == "gemm_v":
         from . import capi
         variant = {"gemv": capi.GEMM_GEMV, "decode": capi.GEMM_DECODE, "tile": capi.GEMM_TILE, "tile_f16": capi.GEMM_TILE_F16,
-                   "decode_tc": capi.GEMM_DECODE_TC}[argv[1]]
+                   "decode_tc": capi.GEMM_DECODE_TC, "gemv_mma": capi.GEMM_GEMV_MMA}[argv[1]]
         M, N, K = map(int, argv[2:5])
         reps = int(argv[5]) if len(argv) > 5 else 5
         xq, xs = _codes(M, K, gen, dev)
