@@ -22,6 +22,23 @@ def test_header_symbols_exported():
     assert lib.wush_abi_version() == 1
 
 
+def test_header_constants_match_the_python_binding():
+    """Variant, quantiser-mode and status numbers of the header are the ones capi.py passes."""
+    from wush_int4_kernel_b200 import capi
+
+    header = open(os.path.join(ROOT, "include", "wush_int4.h")).read()
+    enums = {name: int(value) for name, value in re.findall(r"\b(WUSH_[A-Z0-9_]+)\s*=\s*(-?\d+)", header)}
+    for name, value in enums.items():
+        short = name[len("WUSH_"):]
+        mirror = getattr(capi, short, getattr(capi, name, None))
+        if mirror is not None:
+            assert mirror == value, (name, value, mirror)
+    for name in ("GEMM_AUTO", "GEMM_GEMV", "GEMM_DECODE", "GEMM_TILE", "GEMM_TILE_F16", "GEMM_DECODE_TC", "GEMM_GEMV_MMA",
+                 "TQ_EXACT", "TQ_FAST"):
+        assert enums["WUSH_" + name] == getattr(capi, name), name
+    assert enums["WUSH_OK"] == capi.WUSH_OK == 0 and enums["WUSH_ERR_INVALID_ARGUMENT"] == capi.WUSH_ERR_INVALID_ARGUMENT
+
+
 def test_no_gpu_fails_loudly():
     if torch.cuda.is_available():
         pytest.skip("GPU present")
