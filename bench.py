@@ -43,11 +43,11 @@ sys.path.insert(0, ROOT)
 K_DIM, N_DIM = 8192, 57344
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the product kernel, from the ncu
-# capture summarised in profiles/gemv_dp4a_decode_m1_k8192_n57344.md (264.27 MB read + 3.37 / 4.76 MB
+# capture summarised in profiles/gemv_row_decode_m1_k8192_n57344.md (264.27 MB read + 3.37 / 4.76 MB
 # written in the two captured launches; their mean).
 PRODUCT_KERNEL_DRAM_BYTES = 268_330_000
 PRODUCT_KERNEL_DRAM_SOURCE = ("constant from an earlier ncu capture, not measured in this run: "
-                              "profiles/gemv_dp4a_decode_m1_k8192_n57344.md (scaled by the shard's share of N)")
+                              "profiles/gemv_row_decode_m1_k8192_n57344.md (scaled by the shard's share of N)")
 INT8_NOMINAL_TOPS = 4500.0
 PREFILL_ROWS = 4096
 
