@@ -133,7 +133,7 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
         const auto block_us = [&](double wide) { const double t = 1.2 * wide * unit; return t > 6.0 ? t : 6.0; };
         const int64_t full_blocks = M / 32, rest = M % 32;
         double t_stream = 10.0 + (double)full_blocks * block_us(121.0);
-        if (rest) t_stream += block_us(rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : 121.0);
+        if (rest) t_stream += block_us(rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : rest <= 24 ? 105.0 : 121.0);
         const int split = f16_fused_split(M, N, K);                   // K ranges: the 256-row kernel, also for M <= 128
         const bool wide = M > 128 || split > 1;
         const int64_t units = (wide ? (M + 255) / 256 : 1) * ((N + 255) / 256) * split;

@@ -9,7 +9,7 @@
 // rows; the arithmetic must fit in the shadow of that stream.
 //
 //   * The WEIGHTS are the wide MMA operand: each compute warp owns 16 weight rows (the M=16
-//     side of mma.m16n8k32.s8) against 1, 2 or 4 tiles of 8 activation rows.  The number of
+//     side of mma.m16n8k32.s8) against 1, 2, 3 or 4 tiles of 8 activation rows.  The number of
 //     compute warps per CTA (1..13) is chosen per call so that the whole grid is resident at
 //     once, two CTAs per SM, all with the same number of rows: one balanced wave.
 //   * One more warp is the producer: per stage of 4 groups it issues TMA tile loads of the
@@ -482,9 +482,10 @@ int stream_set_attributes()
     if (int s = resolve_tensor_map_encoder()) return s;
     cudaError_t e;
     if ((e = set_attr<1, false>()) != cudaSuccess || (e = set_attr<2, false>()) != cudaSuccess ||
+        (e = set_attr<3, false>()) != cudaSuccess ||
         (e = set_attr<4, false>()) != cudaSuccess || (e = set_attr<4, true>()) != cudaSuccess ||
         (e = set_attr<1, false, true>()) != cudaSuccess || (e = set_attr<2, false, true>()) != cudaSuccess ||
-        (e = set_attr<4, false, true>()) != cudaSuccess)
+        (e = set_attr<3, false, true>()) != cudaSuccess || (e = set_attr<4, false, true>()) != cudaSuccess)
         return fail(WUSH_ERR_CUDA, "decode kernel: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return WUSH_OK;
 }
@@ -500,6 +501,7 @@ int stream_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const 
 {
     if (M <= 8) return launch_stream<1, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
     if (M <= 16) return launch_stream<2, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
+    if (M <= 24) return launch_stream<3, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
     return launch_stream<4, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
 }
 
@@ -509,6 +511,7 @@ int stream_dispatch_push(const uint8_t* xq, const void* xs, const uint8_t* wq, c
 {
     if (M <= 8) return launch_stream<1, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
     if (M <= 16) return launch_stream<2, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
+    if (M <= 24) return launch_stream<3, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
     if (M <= 32) return launch_stream<4, false, true>(xq, xs, wq, ws, M, N, K, nullptr, nullptr, st, peers);
     return fail(WUSH_ERR_UNSUPPORTED, "w4a4_gemm(decode, pushed): at most 32 rows");
 }
