@@ -88,6 +88,7 @@ int sm_count()
 size_t gemv_smem_bytes(int M, int64_t K);
 int gemv_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
 int mma_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
+int stream_tiles_for(int64_t M, double* relative_cost);
 bool gemv_mma_supported(int64_t M, int64_t N, int64_t K, const void* xs, const void* ws);
 int gemv_mma_dispatch(const uint8_t*, const void*, const uint8_t*, const void*, int64_t, int64_t, int64_t, void*, cudaStream_t);
 bool tc_supported(int64_t M, int64_t N, int64_t K);
@@ -131,9 +132,9 @@ static int resolve_variant(int variant, int64_t M, int64_t N, int64_t K)
         // microseconds from measurements on the 70B gate+up layer (4.7e8 weights) and on narrow layers.
         const double elems = (double)N * (double)K, unit = elems / 4.7e8;
         const auto block_us = [&](double wide) { const double t = 1.2 * wide * unit; return t > 6.0 ? t : 6.0; };
-        const int64_t full_blocks = M / 32, rest = M % 32;
-        double t_stream = 10.0 + (double)full_blocks * block_us(121.0);
-        if (rest) t_stream += block_us(rest <= 8 ? 55.0 : rest <= 16 ? 77.0 : rest <= 24 ? 105.0 : 121.0);
+        double blocks32 = 0.0;                                        // the streaming kernel's blocks of rows, in units of a 32-row block
+        stream_tiles_for(M, &blocks32);
+        const double t_stream = 10.0 + blocks32 * block_us(121.0);
         const int split = f16_fused_split(M, N, K);                   // K ranges: the 256-row kernel, also for M <= 128
         const bool wide = M > 128 || split > 1;
         const int64_t units = (wide ? (M + 255) / 256 : 1) * ((N + 255) / 256) * split;

@@ -496,12 +496,31 @@ bool stream_supported(int64_t K, const void* xs, const void* ws)
     return K % 256 == 0 && aligned16(xs) && aligned16(ws);
 }
 
+// Rows of activations per CTA (8 * tiles) for M rows.  Up to 32 rows: the smallest tile count that holds them.
+// Beyond: every block of rows streams the weights again, so the count of blocks times the measured time of one
+// block (70B layer: 55 / 76 / 105 / 117 us for 1..4 tiles) is what to minimise -- 40 rows are two blocks of 24,
+// not two of 32.  `relative_cost`, if given, receives that product in units of the 4-tile block.
+int stream_tiles_for(int64_t M, double* relative_cost)
+{
+    static const double block_us[5] = {0.0, 55.0, 76.0, 105.0, 117.0};
+    int best = 4;
+    double best_cost = 0.0;
+    for (int mt = 1; mt <= 4; ++mt) {
+        const double cost = (double)((M + 8 * mt - 1) / (8 * mt)) * block_us[mt];
+        if (mt == 1 || cost < best_cost) { best = mt; best_cost = cost; }
+    }
+    if (relative_cost) *relative_cost = best_cost / block_us[4];
+    return best;
+}
+
 int stream_dispatch(const uint8_t* xq, const void* xs, const uint8_t* wq, const void* ws, int64_t M, int64_t N, int64_t K,
                     void* y, cudaStream_t st)
 {
-    if (M <= 8) return launch_stream<1, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
-    if (M <= 16) return launch_stream<2, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
-    if (M <= 24) return launch_stream<3, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
+    switch (stream_tiles_for(M, nullptr)) {
+        case 1: return launch_stream<1, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
+        case 2: return launch_stream<2, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
+        case 3: return launch_stream<3, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
+    }
     return launch_stream<4, false>(xq, xs, wq, ws, M, N, K, y, nullptr, st);
 }
 
