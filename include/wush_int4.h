@@ -295,6 +295,10 @@ int wush_comm_destroy(void* comm);
  * Returns WUSH_OK if every unit is in range, every piece a CTA writes has its own slot below
  * `slots` and the summing kernel adds exactly the written pieces of each cut tile, once each;
  * 101..107, one per broken property, otherwise. */
+/* Activation tiles of 8 rows per CTA that the streaming decode kernel (WUSH_GEMM_DECODE) takes for M rows:
+ * the smallest count that holds them up to 32 rows; beyond, the count minimising (blocks of rows) x
+ * (measured time of a block), since every block streams the weights again.  Host only, no GPU. */
+int wush_debug_stream_tiles(int64_t M);
 int wush_debug_unit_cover(int64_t tiles, int k_steps, int gran, int workers, int force_mode,
                           double step_us, double piece_us, int* cover, int slots, int* plan_out);
 

@@ -66,3 +66,19 @@ def test_switch_disables_the_split(monkeypatch):
 def test_bad_arguments_are_refused():
     lib = capi.load()
     assert lib.wush_debug_unit_cover(0, 8, 1, 148, -1, 0.8, 0.13, None, 296, None) == capi.WUSH_ERR_INVALID_ARGUMENT
+
+
+def test_streaming_kernel_tile_choice():
+    """Up to 32 rows the smallest tile that holds them; beyond, never more padded rows than with 32-row blocks and
+    no more blocks than with 8-row ones -- 40 and 48 rows are two blocks of 24, 64 rows two of 32."""
+    lib = capi.load()
+    tiles = lib.wush_debug_stream_tiles
+    assert [tiles(m) for m in (1, 8, 9, 16, 17, 24, 25, 32)] == [1, 1, 2, 2, 3, 3, 4, 4]
+    assert tiles(40) == 3 and tiles(48) == 3 and tiles(64) == 4 and tiles(72) == 3 and tiles(128) == 4
+    assert tiles(0) == 0
+    for m in range(1, 600):
+        t = tiles(m)
+        assert 1 <= t <= 4
+        blocks = -(-m // (8 * t))
+        assert blocks * 8 * t - m < 32 and blocks <= -(-m // 8)
+        assert blocks * 8 * t <= -(-m // 32) * 32            # never more rows of work than 32-row blocks would do

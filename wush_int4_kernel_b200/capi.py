@@ -51,6 +51,7 @@ SIGNATURES = {
     "wush_comm_gemv_allgather": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "wush_comm_error": (_int, [_vp, ctypes.POINTER(_int)]),
     "wush_comm_destroy": (_int, [_vp]),
+    "wush_debug_stream_tiles": (_int, [_i64]),
     "wush_debug_unit_cover": (_int, [_i64, _int, _int, _int, _int, ctypes.c_double, ctypes.c_double,
                                      ctypes.POINTER(_int), _int, ctypes.POINTER(_int)]),
     "wush_w4a4_gemm_tensor_scale_workspace_bytes": (_sz, [_i64, _i64, _i64]),

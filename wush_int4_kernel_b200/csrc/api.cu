@@ -219,3 +219,7 @@ WUSH_API int wush_w4a4_gemm(const uint8_t* xq, const void* xs, const uint8_t* wq
     }
     return fail(WUSH_ERR_INVALID_ARGUMENT, "w4a4_gemm: unknown variant %d", v);
 }
+
+// Host-side view of a dispatch rule, for the CPU test suite: activation tiles of 8 rows per CTA the streaming kernel
+// takes for M rows.
+WUSH_API int wush_debug_stream_tiles(int64_t M) { return M > 0 ? wush::stream_tiles_for(M, nullptr) : 0; }
