@@ -30,8 +30,8 @@ INT8_NOMINAL_TOPS = 4500.0
 F16_MEASURED_TFLOPS = 1684.0       # cuBLAS bf16 burst measured on this pool: the ceiling of the fp16-folded product
 
 SHAPES = {                      # name -> (K, N, rows per step)
-    "qwen": (4096, 24576, (1, 2, 4, 8, 32)),
-    "llama": (8192, 57344, (1, 2, 3, 4, 8, 16, 32)),
+    "qwen": (4096, 24576, (1, 2, 4, 8, 24, 32)),
+    "llama": (8192, 57344, (1, 2, 3, 4, 8, 16, 24, 32)),
     "mid": (8192, 57344, (64, 128, 256)),
     "square": (4096, 4096, (4096,)),
     "prefill": (8192, 57344, (512, 2048, 4096)),
